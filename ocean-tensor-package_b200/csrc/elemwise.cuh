@@ -1,0 +1,348 @@
+// Elementwise engine: one kernel family for fill (0 inputs), unary, copy/convert
+// (1 input) and binary (2 inputs) operations over up to 8 strided dimensions.
+//
+// It replaces the reference's four macro kernel generators
+// (solid/include/solid/core/gpu/apply_elemwise{1,2,2b,3}.h, variant selection in
+// solid/src/core/gpu/op/apply_elemwise{1,2,3}.c), which issue one scalar access
+// per element and decompose the index with % and / per element.  Here:
+//
+//   ew_contig   every operand is dense along one merged dimension (or a broadcast
+//               scalar): each thread moves VEC elements per operand with 128-bit
+//               ld.global.cs / st.global.cs, UNROLL independent vectors in flight,
+//               64-bit element counts (2^32 elements and beyond);
+//   ew_strided  general case: the innermost dimension is vectorised when every
+//               operand is dense or broadcast along it and rows start on 16-byte
+//               boundaries (VEC > 1), otherwise one element per access (VEC == 1);
+//               outer dimensions are decomposed with multiply-shift division.
+//
+// The operation is an "apply" object A with
+//     A::out_t, A::in1_t, A::in2_t, A::NIN (0, 1 or 2)
+//     out_t A::operator()(in1_t, in2_t) const
+// passed by value, so scalar parameters travel in the kernel arguments.
+//
+// HBM traffic per element = sizeof(out) + sum sizeof(in): every byte is moved once.
+#pragma once
+#include "dtypes.cuh"
+#include "layout.h"
+
+namespace sd {
+
+struct Nothing {};
+
+constexpr int EW_THREADS = 256;
+
+template <int NOPS> struct EwParams {
+   char    *ptr[NOPS];
+   int64_t  stride[NOPS][MAXD];     // bytes; [k][0] is the innermost dimension
+   uint32_t size[MAXD];             // size[0] counts VECTORS in the vectorised variant
+   FastDiv  div[MAXD];
+   int64_t  size64[MAXD];
+   int      ndims;
+   int      wide;                   // 1: total index count needs 64 bits
+   uint64_t total;                  // number of (vector) indices
+   uint64_t nelem;                  // number of elements (ew_contig)
+   uint32_t bcast;                  // bit k: operand k is constant along dimension 0
+   uint32_t unal;                   // bit k: operand k is not aligned to its element size
+};
+
+template <class A> struct ew_traits {
+   static constexpr int NIN = A::NIN;
+   static constexpr int NOPS = NIN + 1;
+   using out_t = typename A::out_t;
+   using in1_t = typename A::in1_t;
+   using in2_t = typename A::in2_t;
+   static constexpr int s_out = (int)sizeof(out_t);
+   static constexpr int s_in1 = NIN >= 1 ? (int)sizeof(in1_t) : s_out;
+   static constexpr int s_in2 = NIN >= 2 ? (int)sizeof(in2_t) : s_out;
+   static constexpr int s_min = s_out < s_in1 ? (s_out < s_in2 ? s_out : s_in2) : (s_in1 < s_in2 ? s_in1 : s_in2);
+   static constexpr int s_max = s_out > s_in1 ? (s_out > s_in2 ? s_out : s_in2) : (s_in1 > s_in2 ? s_in1 : s_in2);
+   // elements per thread-iteration: 16 bytes of the narrowest operand, at most 64 of the widest
+   static constexpr int VEC0 = 16 / s_min > 0 ? 16 / s_min : 1;
+   static constexpr int VEC = (VEC0 * s_max > 64) ? (64 / s_max > 0 ? 64 / s_max : 1) : VEC0;
+   // independent iterations in flight: about 64 bytes per operand and thread
+   static constexpr int UNROLL = (64 / (VEC * s_max)) > 0 ? (64 / (VEC * s_max)) : 1;
+};
+
+// Access to elements that do not start on a multiple of their size (only the copy
+// family accepts such tensors).  Loads fetch the aligned 32-bit words that cover
+// the bytes and realign them with a funnel shift; the word after the last one is
+// touched only when the data really extends into it.  Stores go byte by byte.
+template <class T, int N> SD_D Vec<T, N> ld_unaligned(const char *p)
+{
+   constexpr int B = (int)sizeof(T) * N;
+   Vec<T, N> o;
+   if constexpr (B % 4 == 0) {
+      const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+      const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
+      const uint32_t sh = (uint32_t)(a & 3) * 8;
+      uint32_t w[B / 4 + 1];
+#pragma unroll
+      for (int i = 0; i < B / 4; i++) w[i] = __ldg(q + i);
+      w[B / 4] = sh ? __ldg(q + B / 4) : 0u;
+      uint32_t r[B / 4];
+#pragma unroll
+      for (int i = 0; i < B / 4; i++) r[i] = __funnelshift_r(w[i], w[i + 1], sh);
+      memcpy(&o, r, B);
+   } else {
+      uint8_t r[B];
+#pragma unroll
+      for (int i = 0; i < B; i++) r[i] = __ldg(reinterpret_cast<const uint8_t *>(p) + i);
+      memcpy(&o, r, B);
+   }
+   return o;
+}
+template <class T, int N> SD_D void st_unaligned(char *p, const Vec<T, N> &x)
+{
+   constexpr int B = (int)sizeof(T) * N;
+   uint8_t r[B];
+   memcpy(r, &x, B);
+#pragma unroll
+   for (int i = 0; i < B; i++) reinterpret_cast<uint8_t *>(p)[i] = r[i];
+}
+
+template <class T, int VEC, bool UNAL> SD_D Vec<T, VEC> ew_load(const char *p, bool bcast, bool unal)
+{
+   if (bcast) {
+      T x;
+      if (UNAL && unal) x = ld_unaligned<T, 1>(p).v[0]; else x = ld_one<T>(p);
+      Vec<T, VEC> v;
+#pragma unroll
+      for (int j = 0; j < VEC; j++) v.v[j] = x;
+      return v;
+   }
+   if (UNAL && unal) return ld_unaligned<T, VEC>(p);
+   return ld_vec<T, VEC>(p);
+}
+template <class T, int VEC, bool UNAL> SD_D void ew_store(char *p, const Vec<T, VEC> &x, bool unal)
+{
+   if (UNAL && unal) st_unaligned<T, VEC>(p, x); else st_vec<T, VEC>(p, x);
+}
+
+// ---------------------------------------------------------------------------
+template <class A, bool UNAL>
+__global__ void __launch_bounds__(EW_THREADS) ew_contig(const A apply, const EwParams<A::NIN + 1> p)
+{
+   using X = ew_traits<A>;
+   constexpr int VEC = X::VEC, U = X::UNROLL, NIN = X::NIN;
+   using out_t = typename X::out_t; using in1_t = typename X::in1_t; using in2_t = typename X::in2_t;
+   const uint64_t nvec = p.nelem / VEC;
+   const uint64_t chunk = (uint64_t)EW_THREADS * U;
+   const bool b1 = p.bcast & 1u, b2 = p.bcast & 2u;
+   const bool u1 = p.unal & 1u, u2 = p.unal & 2u, uo = p.unal & (1u << NIN);
+   char *const po = p.ptr[NIN];
+
+   for (uint64_t base = (uint64_t)blockIdx.x * chunk; base < nvec; base += (uint64_t)gridDim.x * chunk) {
+      Vec<in1_t, VEC> a[U]; Vec<in2_t, VEC> b[U];
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+         uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
+         if (i < nvec) {
+            if constexpr (NIN >= 1) a[u] = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + (b1 ? 0 : i * (VEC * sizeof(in1_t))), b1, u1);
+            if constexpr (NIN >= 2) b[u] = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + (b2 ? 0 : i * (VEC * sizeof(in2_t))), b2, u2);
+         }
+      }
+#pragma unroll
+      for (int u = 0; u < U; u++) {
+         uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
+         if (i < nvec) {
+            Vec<out_t, VEC> o;
+#pragma unroll
+            for (int j = 0; j < VEC; j++) o.v[j] = apply(a[u].v[j], b[u].v[j]);
+            ew_store<out_t, VEC, UNAL>(po + i * (VEC * sizeof(out_t)), o, uo);
+         }
+      }
+   }
+   // ragged tail (fewer than VEC elements), one thread each
+   if (VEC > 1 && blockIdx.x == 0) {
+      uint64_t i = nvec * VEC + threadIdx.x;
+      if (i < p.nelem) {
+         in1_t x{}; in2_t y{};
+         if constexpr (NIN >= 1) x = ew_load<in1_t, 1, UNAL>(p.ptr[0] + (b1 ? 0 : i * sizeof(in1_t)), false, u1).v[0];
+         if constexpr (NIN >= 2) y = ew_load<in2_t, 1, UNAL>(p.ptr[1] + (b2 ? 0 : i * sizeof(in2_t)), false, u2).v[0];
+         Vec<out_t, 1> o; o.v[0] = apply(x, y);
+         ew_store<out_t, 1, UNAL>(po + i * sizeof(out_t), o, uo);
+      }
+   }
+}
+
+// ---------------------------------------------------------------------------
+template <class A, int VEC, bool UNAL>
+__global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const EwParams<A::NIN + 1> p)
+{
+   using X = ew_traits<A>;
+   constexpr int NIN = X::NIN, NOPS = NIN + 1;
+   using out_t = typename X::out_t; using in1_t = typename X::in1_t; using in2_t = typename X::in2_t;
+   const bool b1 = p.bcast & 1u, b2 = p.bcast & 2u;
+   const bool u1 = p.unal & 1u, u2 = p.unal & 2u, uo = p.unal & (1u << NIN);
+
+   for (uint64_t idx = (uint64_t)blockIdx.x * EW_THREADS + threadIdx.x; idx < p.total;
+        idx += (uint64_t)gridDim.x * EW_THREADS) {
+      int64_t off[NOPS];
+#pragma unroll
+      for (int k = 0; k < NOPS; k++) off[k] = 0;
+      if (!p.wide) {
+         uint32_t r = (uint32_t)idx;
+         for (int d = 0; d < p.ndims - 1; d++) {
+            uint32_t q = fastdiv(r, p.div[d]);
+            uint32_t c = r - q * p.size[d];
+            r = q;
+#pragma unroll
+            for (int k = 0; k < NOPS; k++) off[k] += (int64_t)c * p.stride[k][d];
+         }
+#pragma unroll
+         for (int k = 0; k < NOPS; k++) off[k] += (int64_t)r * p.stride[k][p.ndims - 1];
+      } else {
+         uint64_t r = idx;
+         for (int d = 0; d < p.ndims - 1; d++) {
+            uint64_t q = r / (uint64_t)p.size64[d];
+            uint64_t c = r - q * (uint64_t)p.size64[d];
+            r = q;
+#pragma unroll
+            for (int k = 0; k < NOPS; k++) off[k] += (int64_t)c * p.stride[k][d];
+         }
+#pragma unroll
+         for (int k = 0; k < NOPS; k++) off[k] += (int64_t)r * p.stride[k][p.ndims - 1];
+      }
+      Vec<in1_t, VEC> a; Vec<in2_t, VEC> b;
+      if constexpr (NIN >= 1) a = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + off[0], VEC > 1 && b1, u1);
+      if constexpr (NIN >= 2) b = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + off[1], VEC > 1 && b2, u2);
+      Vec<out_t, VEC> o;
+#pragma unroll
+      for (int j = 0; j < VEC; j++) o.v[j] = apply(a.v[j], b.v[j]);
+      ew_store<out_t, VEC, UNAL>(p.ptr[NIN] + off[NIN], o, uo);
+   }
+}
+
+// ---------------------------------------------------------------------------
+// Host side: pick the variant and launch.
+// ---------------------------------------------------------------------------
+inline int ew_grid(uint64_t work_items, uint64_t items_per_block, const DeviceInfo &dev)
+{
+   uint64_t blocks = (work_items + items_per_block - 1) / items_per_block;
+   uint64_t cap = (uint64_t)dev.sms * (dev.max_threads_per_sm / EW_THREADS) * 4;   // a few waves, whole SM multiples
+   if (blocks > cap) blocks = cap;
+   if (blocks < 1) blocks = 1;
+   return (int)blocks;
+}
+
+template <class A, bool ALLOW_UNALIGNED = false>
+int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
+{
+   using X = ew_traits<A>;
+   constexpr int NIN = X::NIN, NOPS = NIN + 1, VEC = X::VEC;
+   const int esize[3] = { NIN >= 1 ? X::s_in1 : X::s_out, NIN >= 2 ? X::s_in2 : X::s_out, X::s_out };
+   auto es = [&](int k) { return k == NIN ? X::s_out : esize[k]; };
+   if (L.nelem == 0) return 0;
+   DeviceInfo dev;
+   if (current_device_info(&dev) != 0) return -1;
+
+   EwParams<NOPS> p;
+   memset(&p, 0, sizeof(p));
+   for (int k = 0; k < NOPS; k++) p.ptr[k] = L.ptr[k];
+   p.nelem = (uint64_t)L.nelem;
+
+   // dense (or broadcast) along dimension 0 for every operand?
+   bool dense0 = true; uint32_t bcast = 0;
+   for (int k = 0; k < NOPS; k++) {
+      if (L.stride[k][0] == es(k) || L.size[0] == 1) continue;
+      if (L.stride[k][0] == 0 && k != NIN) { bcast |= (1u << k); continue; }
+      dense0 = false;
+   }
+   // vector accesses need 16-byte aligned addresses (or the natural alignment of a narrower vector)
+   auto vec_align = [&](int k) { int b = es(k) * VEC; return (size_t)(b >= 16 ? 16 : b); };
+   // operands whose addresses are not multiples of the element size
+   uint32_t unal = 0;
+   for (int k = 0; k < NOPS; k++) {
+      bool bad = !aligned_to(L.ptr[k], (size_t)es(k));
+      for (int d = 0; d < L.ndims && !bad; d++) if (L.stride[k][d] % es(k) != 0) bad = true;
+      if (bad) unal |= (1u << k);
+   }
+   if (unal && !ALLOW_UNALIGNED) SD_ERROR("Tensor data must be aligned to the element size");
+   p.unal = unal;
+   bool aligned = true;
+   for (int k = 0; k < NOPS; k++) {
+      if ((bcast | unal) & (1u << k)) continue;
+      if (!aligned_to(L.ptr[k], vec_align(k))) aligned = false;
+   }
+
+   if (L.ndims == 1 && dense0 && (aligned || VEC == 1)) {
+      p.bcast = bcast;
+      uint64_t nvec = p.nelem / VEC;
+      int grid = ew_grid(nvec ? nvec : 1, (uint64_t)EW_THREADS * X::UNROLL, dev);
+      if (ALLOW_UNALIGNED && unal) ew_contig<A, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else                         ew_contig<A, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      SD_LAUNCH_CHECK();
+      return 0;
+   }
+
+   // strided: can the innermost dimension be vectorised?
+   bool vec_ok = dense0 && aligned && VEC > 1 && (L.size[0] % VEC == 0);
+   if (vec_ok) for (int k = 0; k < NOPS && vec_ok; k++) {
+      if ((bcast | unal) & (1u << k)) continue;
+      for (int d = 1; d < L.ndims; d++) if (L.stride[k][d] % (int64_t)vec_align(k) != 0) { vec_ok = false; break; }
+   }
+   const int vec = vec_ok ? VEC : 1;
+   p.ndims = L.ndims;
+   p.bcast = vec_ok ? bcast : 0;
+   uint64_t total = 1; bool fits32 = true;
+   for (int d = 0; d < L.ndims; d++) {
+      int64_t sz = (d == 0) ? L.size[0] / vec : L.size[d];
+      p.size64[d] = sz;
+      if (sz > 0x7FFFFFFFll) fits32 = false;
+      p.size[d] = (uint32_t)sz;
+      p.div[d] = make_fastdiv((uint32_t)sz);
+      total *= (uint64_t)sz;
+      for (int k = 0; k < NOPS; k++) p.stride[k][d] = (d == 0) ? L.stride[k][0] * vec : L.stride[k][d];
+   }
+   p.total = total;
+   p.wide = (total > 0xFFFFFFFFull || !fits32) ? 1 : 0;
+   int grid = ew_grid(total, EW_THREADS, dev);
+   if (ALLOW_UNALIGNED && unal) {
+      if (vec_ok) ew_strided<A, VEC, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else        ew_strided<A, 1, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+   } else {
+      if (vec_ok) ew_strided<A, VEC, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else        ew_strided<A, 1, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+   }
+   SD_LAUNCH_CHECK();
+   return 0;
+}
+
+// ---------------------------------------------------------------------------
+// Apply adaptors for the functors of ops_unary.cuh / ops_binary.cuh
+// ---------------------------------------------------------------------------
+template <class Op, class T> struct UnaryApply {
+   static constexpr int NIN = 1;
+   using in1_t = T; using in2_t = Nothing; using out_t = typename Op::template out<T>;
+   SD_D out_t operator()(T x, Nothing) const { return Op::template f<T>(x); }
+};
+template <class Op, class T> struct BinaryApply {
+   static constexpr int NIN = 2;
+   using in1_t = T; using in2_t = typename Op::template in2<T>; using out_t = typename Op::template out<T>;
+   SD_D out_t operator()(in1_t x, in2_t y) const { return Op::template f<T>(x, y); }
+};
+
+template <class Op, class T>
+int launch_unary(int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1,
+                 const ptrdiff_t *strides2, void *ptr2, cudaStream_t stream)
+{
+   if (strides2 == nullptr && ptr2 == nullptr) { strides2 = strides1; ptr2 = ptr1; }   // in place
+   const ptrdiff_t *st[2] = { strides1, strides2 }; void *pt[2] = { ptr1, ptr2 };
+   Layout<2> L;
+   if (make_layout<2>(L, ndims, size, st, pt, 1) != 0) return -1;
+   return ew_launch(UnaryApply<Op, T>(), L, stream);
+}
+
+template <class Op, class T>
+int launch_binary(int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1,
+                  const ptrdiff_t *strides2, void *ptr2, const ptrdiff_t *strides3, void *ptr3,
+                  cudaStream_t stream)
+{
+   if (strides3 == nullptr && ptr3 == nullptr) { strides3 = strides1; ptr3 = ptr1; }   // into operand 1
+   const ptrdiff_t *st[3] = { strides1, strides2, strides3 }; void *pt[3] = { ptr1, ptr2, ptr3 };
+   Layout<3> L;
+   if (make_layout<3>(L, ndims, size, st, pt, 2) != 0) return -1;
+   return ew_launch(BinaryApply<Op, T>(), L, stream);
+}
+
+} // namespace sd

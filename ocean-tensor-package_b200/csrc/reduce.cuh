@@ -1,0 +1,396 @@
+// Reduction engine: global and per-axis reductions share three kernels plus a
+// finalize pass.  A global reduction is the per-axis problem with one output.
+//
+// Replaces solid/include/solid/core/gpu/reduce_all.h:136-274 (512-entry volatile
+// shared-memory tree, one scalar load per thread-iteration, 1-warp finalize) and
+// reduce_axis.h:142-519 (thread / warp / block modes, all with per-element
+// index decomposition and scalar loads).
+//
+//   red_row   the first reduced dimension is dense in memory: a group of 32 or 256
+//             threads sweeps each output's data with 128-bit loads, four vectors in
+//             flight per thread; warp-shuffle tree, then a fixed-order fold of the
+//             warp results through shared memory;
+//   red_col   the first kept dimension is dense: each thread owns VEC adjacent
+//             outputs and walks the reduced range, so a warp still reads whole
+//             128-byte lines; blockDim.y slices the range and is folded in order;
+//   red_gen   anything else: one thread per output, full index decomposition;
+//   red_fin   when the reduced range of an output was split over several blocks
+//             (few outputs, e.g. the global case) the blocks write partial
+//             accumulators to scratch memory and this second pass folds them in
+//             index order and applies the finalize step.  There is no atomic and
+//             no inter-block wait, so results are bit-reproducible for a given
+//             device and shape.
+//
+// HBM traffic: every input element is read once; partials are a few KB.
+#pragma once
+#include "dtypes.cuh"
+#include "layout.h"
+
+namespace sd {
+
+constexpr int RED_THREADS = 256;
+
+struct RedParams {
+   char    *src, *dst, *buf;
+   int      ndims, rdims;
+   int64_t  size[MAXD], stride1[MAXD], stride2[MAXD];
+   int64_t  rsize[MAXD], rstride[MAXD];
+   uint64_t nout, relem;
+   uint32_t split;          // blocks (or groups) that share one output
+   uint32_t group;          // red_row: threads per output chunk (32 or 256)
+   uint64_t tiles0;         // red_col: tiles along outer dimension 0
+};
+
+// offset of output `o` in source (outer part) and destination
+SD_D void outer_offsets(const RedParams &p, uint64_t o, int64_t &off1, int64_t &off2)
+{
+   off1 = 0; off2 = 0;
+   for (int d = 0; d < p.ndims - 1; d++) {
+      uint64_t q = o / (uint64_t)p.size[d]; uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
+      off1 += (int64_t)c * p.stride1[d]; off2 += (int64_t)c * p.stride2[d];
+   }
+   if (p.ndims > 0) { off1 += (int64_t)o * p.stride1[p.ndims - 1]; off2 += (int64_t)o * p.stride2[p.ndims - 1]; }
+}
+// offset of reduced index r, decomposed over reduced dimensions first..rdims-1
+SD_D int64_t reduced_offset(const RedParams &p, uint64_t r, int first)
+{
+   int64_t off = 0;
+   for (int d = first; d < p.rdims - 1; d++) {
+      uint64_t q = r / (uint64_t)p.rsize[d]; uint64_t c = r - q * (uint64_t)p.rsize[d]; r = q;
+      off += (int64_t)c * p.rstride[d];
+   }
+   if (p.rdims > first) off += (int64_t)r * p.rstride[p.rdims - 1];
+   return off;
+}
+
+template <class V> SD_D V shfl_down_any(const V &x, int delta)
+{
+   constexpr int W = (sizeof(V) + 3) / 4;
+   uint32_t w[W] = {0};
+   memcpy(w, &x, sizeof(V));
+#pragma unroll
+   for (int i = 0; i < W; i++) w[i] = __shfl_down_sync(0xFFFFFFFFu, w[i], delta);
+   V y; memcpy(&y, w, sizeof(V));
+   return y;
+}
+
+// Fold the accumulators of `width` consecutive lanes into the first lane.
+template <class R, class A> SD_D void warp_fold(const R &r, A &acc, int width = 32)
+{
+#pragma unroll
+   for (int d = 16; d >= 1; d >>= 1) {
+      A other = shfl_down_any<A>(acc, d);
+      if (d < width) r.combine(acc, other);
+   }
+}
+
+// Fold one accumulator per thread of the block into thread 0 (fixed order).
+template <class R, class A> SD_D void block_fold(const R &r, A &acc, A *smem)
+{
+   warp_fold(r, acc);
+   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x * blockDim.y) >> 5;
+   if (lane == 0) smem[warp] = acc;
+   __syncthreads();
+   if (threadIdx.x == 0) for (int w = 1; w < nwarps; w++) r.combine(acc, smem[w]);
+}
+
+template <class R, class T> SD_D typename R::acc_t red_start(const R &r, const char *first_elem)
+{
+   if constexpr (R::seeded) return r.seed(ld_one<T>(first_elem));
+   else { (void)first_elem; return r.init(); }
+}
+
+template <class R> SD_D void red_emit(const R &r, const RedParams &p, uint64_t out, uint32_t s,
+                                      int64_t off2, const typename R::acc_t &acc)
+{
+   using A = typename R::acc_t; using O = typename R::out_t;
+   if (p.split > 1) reinterpret_cast<A *>(p.buf)[out * p.split + s] = acc;
+   else *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
+}
+
+// ---------------------------------------------------------------------------
+template <class R, class T, int VEC>
+__global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParams p)
+{
+   using A = typename R::acc_t;
+   __shared__ A smem[RED_THREADS / 32];
+   const uint32_t group = p.group;
+   const uint32_t gpb = RED_THREADS / group;
+   const uint64_t gid = (uint64_t)blockIdx.x * gpb + threadIdx.x / group;
+   const uint32_t lane = threadIdx.x % group;
+   const uint64_t out = gid / p.split;
+   const uint32_t s = (uint32_t)(gid - out * p.split);
+   const bool live = out < p.nout;
+
+   int64_t off1 = 0, off2 = 0;
+   if (live) outer_offsets(p, out, off1, off2);
+   const char *base = p.src + off1;
+   A acc = red_start<R, T>(r, live ? base : p.src);
+
+   if (live) {
+      const uint64_t rowlen = (uint64_t)p.rsize[0];
+      const uint64_t nslot = (rowlen + VEC - 1) / VEC;              // vector slots per row (last may be ragged)
+      const uint64_t rows = p.relem / rowlen;
+      const uint64_t total = rows * nslot;
+      const uint64_t chunk = (total + p.split - 1) / p.split;
+      const uint64_t begin = (uint64_t)s * chunk;
+      const uint64_t end = begin + chunk < total ? begin + chunk : total;
+      constexpr int U = 4;
+      for (uint64_t slot0 = begin + lane; slot0 < end; slot0 += (uint64_t)group * U) {
+         Vec<T, VEC> v[U]; int cnt[U];
+#pragma unroll
+         for (int u = 0; u < U; u++) {
+            uint64_t slot = slot0 + (uint64_t)u * group;
+            cnt[u] = 0;
+            if (slot < end) {
+               uint64_t row = 0, j = slot;
+               if (rows > 1) { row = slot / nslot; j = slot - row * nslot; }
+               const char *q = base + (rows > 1 ? reduced_offset(p, row, 1) : 0) + (int64_t)(j * VEC * sizeof(T));
+               uint64_t left = rowlen - j * VEC;
+               if (VEC == 1 || left >= (uint64_t)VEC) { v[u] = ld_vec<T, VEC>(q); cnt[u] = VEC; }
+               else { cnt[u] = (int)left;
+#pragma unroll
+                  for (int e = 0; e < VEC; e++) if (e < (int)left) v[u].v[e] = ld_one<T>(q + e * sizeof(T)); }
+            }
+         }
+#pragma unroll
+         for (int u = 0; u < U; u++) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) if (e < cnt[u]) r.accum(acc, v[u].v[e]);
+         }
+      }
+   }
+   // fold the group
+   if (group == 32) {
+      warp_fold(r, acc);
+      if (lane == 0 && live) red_emit(r, p, out, s, off2, acc);
+   } else {
+      block_fold(r, acc, smem);
+      if (threadIdx.x == 0 && live) red_emit(r, p, out, s, off2, acc);
+   }
+}
+
+// ---------------------------------------------------------------------------
+// blockDim = (32, 8): x owns VEC adjacent outputs along outer dimension 0, y slices
+// the reduced range.
+template <class R, class T, int VEC>
+__global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParams p)
+{
+   using A = typename R::acc_t;
+   __shared__ A smem[8][32][VEC];
+   uint64_t bid = blockIdx.x;
+   const uint32_t s = (uint32_t)(bid % p.split); bid /= p.split;
+   const uint64_t tile = bid % p.tiles0; const uint64_t rest = bid / p.tiles0;
+   const uint64_t o0 = (tile * 32 + threadIdx.x) * VEC;                 // first of my outputs along dim 0
+   const bool live = o0 < (uint64_t)p.size[0];
+   const int nmine = live ? (int)(((uint64_t)p.size[0] - o0) < (uint64_t)VEC ? ((uint64_t)p.size[0] - o0) : VEC) : 0;
+
+   // offsets of the outer dimensions 1.. (dimension 0 is dense)
+   int64_t off1 = 0, off2 = 0;
+   {  uint64_t o = rest;
+      for (int d = 1; d < p.ndims - 1; d++) {
+         uint64_t q = o / (uint64_t)p.size[d]; uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
+         off1 += (int64_t)c * p.stride1[d]; off2 += (int64_t)c * p.stride2[d]; }
+      if (p.ndims > 1) { off1 += (int64_t)o * p.stride1[p.ndims - 1]; off2 += (int64_t)o * p.stride2[p.ndims - 1]; }
+   }
+   const char *base = p.src + off1 + (int64_t)(o0 * sizeof(T));
+   A acc[VEC];
+#pragma unroll
+   for (int e = 0; e < VEC; e++) acc[e] = red_start<R, T>(r, (e < nmine) ? base + e * sizeof(T) : p.src);
+
+   const uint64_t chunk = (p.relem + p.split - 1) / p.split;
+   const uint64_t begin = (uint64_t)s * chunk;
+   const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
+   if (live) {
+      constexpr int U = 4;
+      for (uint64_t r0 = begin + threadIdx.y; r0 < end; r0 += (uint64_t)blockDim.y * U) {
+         Vec<T, VEC> v[U]; bool ok[U];
+#pragma unroll
+         for (int u = 0; u < U; u++) {
+            uint64_t rr = r0 + (uint64_t)u * blockDim.y;
+            ok[u] = rr < end;
+            if (ok[u]) {
+               const char *q = base + (p.rdims == 1 ? (int64_t)rr * p.rstride[0] : reduced_offset(p, rr, 0));
+               if (nmine == VEC) v[u] = ld_vec<T, VEC>(q);
+               else {
+#pragma unroll
+                  for (int e = 0; e < VEC; e++) if (e < nmine) v[u].v[e] = ld_one<T>(q + e * sizeof(T)); }
+            }
+         }
+#pragma unroll
+         for (int u = 0; u < U; u++) if (ok[u]) {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) if (e < nmine) r.accum(acc[e], v[u].v[e]);
+         }
+      }
+   }
+#pragma unroll
+   for (int e = 0; e < VEC; e++) smem[threadIdx.y][threadIdx.x][e] = acc[e];
+   __syncthreads();
+   if (threadIdx.y == 0 && live) {
+      for (int y = 1; y < (int)blockDim.y; y++) {
+#pragma unroll
+         for (int e = 0; e < VEC; e++) r.combine(acc[e], smem[y][threadIdx.x][e]);
+      }
+      const uint64_t outbase = rest * (uint64_t)p.size[0] + o0;
+#pragma unroll
+      for (int e = 0; e < VEC; e++) if (e < nmine)
+         red_emit(r, p, outbase + e, s, off2 + (int64_t)(o0 + e) * p.stride2[0], acc[e]);
+   }
+}
+
+// ---------------------------------------------------------------------------
+template <class R, class T>
+__global__ void __launch_bounds__(RED_THREADS) red_gen(const R r, const RedParams p)
+{
+   using A = typename R::acc_t;
+   const uint64_t gid = (uint64_t)blockIdx.x * RED_THREADS + threadIdx.x;
+   const uint64_t out = gid / p.split;
+   const uint32_t s = (uint32_t)(gid - out * p.split);
+   if (out >= p.nout) return;
+   int64_t off1, off2;
+   outer_offsets(p, out, off1, off2);
+   const char *base = p.src + off1;
+   A acc = red_start<R, T>(r, base);
+   const uint64_t chunk = (p.relem + p.split - 1) / p.split;
+   const uint64_t begin = (uint64_t)s * chunk;
+   const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
+   for (uint64_t rr = begin; rr < end; rr++) r.accum(acc, ld_one<T>(base + reduced_offset(p, rr, 0)));
+   red_emit(r, p, out, s, off2, acc);
+}
+
+// ---------------------------------------------------------------------------
+// One warp per output folds its `split` partials: lane l takes partials l, l+32, ...
+// in order, then the lanes are folded by the shuffle tree.
+template <class R>
+__global__ void __launch_bounds__(RED_THREADS) red_fin(const R r, const RedParams p)
+{
+   using A = typename R::acc_t; using O = typename R::out_t;
+   const uint64_t out = (uint64_t)blockIdx.x * (RED_THREADS / 32) + (threadIdx.x >> 5);
+   const uint32_t lane = threadIdx.x & 31;
+   const bool live = out < p.nout;
+   const A *part = reinterpret_cast<const A *>(p.buf) + (live ? out : 0) * p.split;
+   A acc = part[lane < p.split ? lane : 0];          // an extra copy of a partial is harmless only for
+   bool have = lane < p.split;                        // idempotent folds, so lanes without one are skipped below
+   for (uint32_t i = lane + 32; i < p.split; i += 32) r.combine(acc, part[i]);
+   // shuffle tree over the lanes that hold data
+#pragma unroll
+   for (int d = 16; d >= 1; d >>= 1) {
+      A other = shfl_down_any<A>(acc, d);
+      bool other_has = __shfl_down_sync(0xFFFFFFFFu, (int)have, d) != 0 && (lane + d < 32);
+      if (have && other_has) r.combine(acc, other);
+   }
+   if (lane == 0 && live) {
+      int64_t off1, off2;
+      outer_offsets(p, out, off1, off2);
+      *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
+   }
+}
+
+// ---------------------------------------------------------------------------
+// Planning (host)
+// ---------------------------------------------------------------------------
+struct RedPlan {
+   RedParams p;
+   uint32_t  split_cap;     // upper bound on split used to size the scratch buffer
+};
+
+// Largest number of blocks that may share one output, from the shape alone.
+inline uint32_t red_split_cap(uint64_t nout, uint64_t relem, int sms)
+{
+   uint64_t by_work = relem / 256; if (by_work < 1) by_work = 1;
+   uint64_t tiles = nout / 512; if (tiles < 1) tiles = 1;
+   uint64_t by_fill = ((uint64_t)sms * 8 + tiles - 1) / tiles;
+   uint64_t cap = by_work < by_fill ? by_work : by_fill;
+   if (cap < 1) cap = 1;
+   if (cap > 65535) cap = 65535;
+   return (uint32_t)cap;
+}
+
+// Normalise outer and reduced dimensions (sizes, strides in bytes).
+inline int red_make_params(RedParams &p, int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1,
+                           const ptrdiff_t *strides2, void *ptr2, int rdims, const size_t *rsize,
+                           const ptrdiff_t *rstrides)
+{
+   memset(&p, 0, sizeof(p));
+   Layout<2> LO; Layout<1> LR;
+   const ptrdiff_t zero[MAXD] = {0};
+   {  const ptrdiff_t *st[2] = { strides1, strides2 ? strides2 : zero }; void *pt[2] = { ptr1, ptr2 };
+      if (make_layout<2>(LO, ndims, size, st, pt, -1) != 0) return -1; }
+   char *src = LO.ptr[0];
+   {  const ptrdiff_t *st[1] = { rstrides }; void *pt[1] = { src };
+      if (make_layout<1>(LR, rdims, rsize, st, pt, 0) != 0) return -1; }
+   p.src = LR.ptr[0]; p.dst = LO.ptr[1];
+   p.nout = (uint64_t)LO.nelem; p.relem = (uint64_t)LR.nelem;
+   p.ndims = LO.nelem ? LO.ndims : 0; p.rdims = LR.nelem ? LR.ndims : 0;
+   for (int d = 0; d < p.ndims; d++) { p.size[d] = LO.size[d]; p.stride1[d] = LO.stride[0][d]; p.stride2[d] = LO.stride[1][d]; }
+   for (int d = 0; d < p.rdims; d++) { p.rsize[d] = LR.size[d]; p.rstride[d] = LR.stride[0][d]; }
+   return 0;
+}
+
+template <class R, class T>
+int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
+{
+   using A = typename R::acc_t;
+   constexpr int VEC = 16 / (int)sizeof(T) > 0 ? 16 / (int)sizeof(T) : 1;
+   if (p.nout == 0 || p.relem == 0) return 0;
+   DeviceInfo dev;
+   if (current_device_info(&dev) != 0) return -1;
+   if (!aligned_to(p.src, sizeof(T))) SD_ERROR("Tensor data must be aligned to the element size");
+   const uint64_t want = (uint64_t)dev.sms * 8;
+   auto pick_split = [&](uint64_t units) {
+      uint64_t s = (want + units - 1) / units; if (s < 1) s = 1;
+      if (s > split_cap) s = split_cap; return (uint32_t)s; };
+   if (!p.buf) split_cap = 1;
+
+   const bool row_dense = p.rdims >= 1 && p.rstride[0] == (int64_t)sizeof(T) && p.rsize[0] >= 16;
+   const bool col_dense = p.ndims >= 1 && p.stride1[0] == (int64_t)sizeof(T) && p.size[0] >= 16;
+   int fin_needed = 0;
+
+   if (row_dense && (p.rsize[0] >= 128 || !col_dense)) {
+      // can whole vectors be loaded?  every row start must sit on a 16-byte boundary
+      bool vec = VEC > 1 && aligned_to(p.src, 16);
+      for (int d = 0; d < p.ndims && vec; d++) if (p.stride1[d] % 16 != 0) vec = false;
+      for (int d = 1; d < p.rdims && vec; d++) if (p.rstride[d] % 16 != 0) vec = false;
+      p.group = (p.relem >= 2048) ? 256 : 32;
+      p.split = pick_split(p.nout * (p.group / 32) / 8 + 1);
+      uint64_t groups = p.nout * p.split;
+      uint64_t gpb = RED_THREADS / p.group;
+      uint64_t blocks = (groups + gpb - 1) / gpb;
+      if (blocks > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
+      if (vec) red_row<R, T, VEC><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      else     red_row<R, T, 1><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      fin_needed = p.split > 1;
+   } else if (col_dense) {
+      bool vec = VEC > 1 && aligned_to(p.src, 16);
+      for (int d = 1; d < p.ndims && vec; d++) if (p.stride1[d] % 16 != 0) vec = false;
+      for (int d = 0; d < p.rdims && vec; d++) if (p.rstride[d] % 16 != 0) vec = false;
+      const int v = vec ? VEC : 1;
+      p.tiles0 = ((uint64_t)p.size[0] + 32 * v - 1) / (32 * v);
+      uint64_t rest = p.nout / (uint64_t)p.size[0];
+      p.split = pick_split(p.tiles0 * rest);
+      uint64_t blocks = p.tiles0 * rest * p.split;
+      if (blocks > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
+      dim3 bd(32, 8);
+      if (vec) red_col<R, T, VEC><<<(unsigned)blocks, bd, 0, stream>>>(r, p);
+      else     red_col<R, T, 1><<<(unsigned)blocks, bd, 0, stream>>>(r, p);
+      fin_needed = p.split > 1;
+   } else {
+      p.split = pick_split(p.nout / RED_THREADS + 1);
+      uint64_t threads = p.nout * p.split;
+      uint64_t blocks = (threads + RED_THREADS - 1) / RED_THREADS;
+      if (blocks > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
+      red_gen<R, T><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      fin_needed = p.split > 1;
+   }
+   SD_LAUNCH_CHECK();
+   if (fin_needed) {
+      uint64_t blocks = (p.nout + (RED_THREADS / 32) - 1) / (RED_THREADS / 32);
+      red_fin<R><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      SD_LAUNCH_CHECK();
+   }
+   (void)sizeof(A);
+   return 0;
+}
+
+} // namespace sd

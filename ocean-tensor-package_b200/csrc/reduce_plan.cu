@@ -1,0 +1,89 @@
+// Type-independent parts of the reduction interface: scratch sizes, the axis
+// reduction planner and the device-resident form of the global reductions.
+// Counterparts: solid/src/core/gpu/op/reduce_all.c:77-123 (buffer size),
+// solid/src/core/gpu/op/reduce_axis.c:22-315 (solid_gpu_reduce_axis_prepare).
+#include <cstring>
+#include "solid_core_gpu.h"
+#include "reduce.cuh"
+
+namespace sd { thread_local void *reduce_all_device_result = nullptr; }
+
+// 16 bytes for the result slot, then one accumulator (at most 16 bytes) per block
+// that can share the single output.
+extern "C" int solid_gpu_reduce_all_buffer_size(size_t nelem, int device, size_t *size)
+{
+   solid_gpu_properties *prop = solid_gpu_get_device_properties(device);
+   if (prop == nullptr) return -1;
+   uint32_t cap = sd::red_split_cap(1, nelem, prop->multiprocessor_count);
+   *size = 16 + (size_t)cap * 16;
+   return 0;
+}
+
+// Record the tensors and decide how much scratch the launch may use.  The kernel
+// family itself is chosen at launch time, when the element type is known; only
+// the bound on blocks-per-output has to be fixed here because it sizes the
+// buffer: bufferSize = outputs * split * elemsize, or 0 when every output is
+// produced by a single block.
+extern "C" int solid_gpu_reduce_axis_prepare(solid_gpu_reduce_axis_config *config, int elemsize,
+                                             int ndims, const size_t *size, const ptrdiff_t *strides1,
+                                             void *ptr1, const ptrdiff_t *strides2, void *ptr2,
+                                             int rdims, const size_t *rsize, const ptrdiff_t *rstrides,
+                                             cudaStream_t stream)
+{
+   if (ndims < 0 || ndims > SOLID_MAX_TENSOR_DIMS || rdims < 0 || rdims > SOLID_MAX_TENSOR_DIMS)
+      SD_ERROR("Number of dimensions exceeds the maximum of %d", SOLID_MAX_TENSOR_DIMS);
+   if (elemsize <= 0 || elemsize > 16) SD_ERROR("Invalid accumulator size %d", elemsize);
+   sd::DeviceInfo dev;
+   if (sd::current_device_info(&dev) != 0) return -1;
+   memset(config, 0, sizeof(*config));
+   solid_gpu_reduce_axis_data &d = config->data;
+   size_t nelem = 1, relem = 1;
+   for (int i = 0; i < ndims; i++) { d.size[i] = size[i]; d.strides1[i] = strides1[i]; d.strides2[i] = strides2[i]; nelem *= size[i]; }
+   for (int i = 0; i < rdims; i++) { d.rsize[i] = rsize[i]; d.rstrides[i] = rstrides[i]; relem *= rsize[i]; }
+   d.ptr1 = (char *)ptr1; d.ptr2 = (char *)ptr2; d.ptrBuffer = nullptr;
+   d.nelem = nelem; d.relem = relem; d.ndims = ndims; d.rdims = rdims;
+   uint32_t cap = (nelem && relem) ? sd::red_split_cap(nelem, relem, dev.sms) : 1;
+   config->mode = cap > 1 ? 3 : 2;                 // 3: partials + finalize pass, 2: single pass
+   config->sharedMem = cap;                        // read back by solid_gpu_axis_<op>_<type>
+   config->sharedMemFinalize = (size_t)elemsize;
+   config->bufferSize = cap > 1 ? (size_t)nelem * cap * (size_t)elemsize : 0;
+   config->blockSize = dim3(sd::RED_THREADS, 1, 1);
+   config->gridSize = dim3(1, 1, 1);
+   config->blockSizeFinalize = dim3(sd::RED_THREADS, 1, 1);
+   config->gridSizeFinalize = dim3(1, 1, 1);
+   config->stream = stream;
+   return 0;
+}
+
+// Device-resident global reduction: look the operation up by name and run it
+// with the result slot redirected to `result` (device memory).
+namespace {
+struct NamedTable { const char *name; void *const *table; int kind; };   // kind 0: bool, 1: uint64, 2: void result
+#define SD_NAMED(KIND, NAME, GROUP) { #NAME, (void *const *)solid_gpu_##NAME, KIND },
+#define SD_NAMED_BOOL(NAME, GROUP) SD_NAMED(0, NAME, GROUP)
+#define SD_NAMED_U64(NAME, GROUP)  SD_NAMED(1, NAME, GROUP)
+#define SD_NAMED_VOID(NAME, GROUP) SD_NAMED(2, NAME, GROUP)
+const NamedTable named_tables[] = {
+   SOLID_GPU_REDUCE_BOOL_OPS(SD_NAMED_BOOL)
+   SOLID_GPU_REDUCE_U64_OPS(SD_NAMED_U64)
+   SOLID_GPU_REDUCE_VOID_OPS(SD_NAMED_VOID)
+};
+} // namespace
+
+extern "C" int solid_gpu_reduce_all_device(const char *op, int dtype, SOLID_GPU_ARGS_REDUCE_HEAD,
+                                           void *result, void *buffer, cudaStream_t stream)
+{
+   if (dtype < 0 || dtype >= SOLID_NUM_TYPES) SD_ERROR("Invalid type index %d", dtype);
+   if (result == nullptr) SD_ERROR("Device result pointer is NULL");
+   for (const NamedTable &t : named_tables) {
+      if (strcmp(t.name, op) != 0) continue;
+      void *fn = t.table[dtype];
+      if (fn == nullptr) SD_ERROR("Reduction '%s' is not available for type index %d", op, dtype);
+      sd::reduce_all_device_result = result;
+      // the three signatures differ only in the static type of the result pointer
+      int status = ((solid_funptr_gpu_sum)fn)(ndims, size, strides, ptr, nullptr, buffer, stream);
+      sd::reduce_all_device_result = nullptr;
+      return status;
+   }
+   SD_ERROR("Unknown reduction '%s'", op);
+}

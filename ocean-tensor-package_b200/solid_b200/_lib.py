@@ -1,0 +1,218 @@
+"""ctypes binding of libsolid_core_gpu.so (the C-ABI declared in include/solid_core_gpu.h).
+
+There is no fallback: if the library has not been built, importing this module
+raises.  Pointers are plain integers (device addresses), sizes and strides are
+Python sequences; strides are in bytes.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+from . import dtypes as dt
+from . import oplist as ol
+
+LIB_PATH = Path(__file__).resolve().parent.parent / "lib" / "libsolid_core_gpu.so"
+
+
+class SolidError(RuntimeError):
+    """A Solid entry point returned -1; the message is the library's solid_errmsg."""
+
+
+class Scalar(C.Union):
+    """solid_scalar (solid/include/solid/base/generic/scalar.h:27-43): 16 bytes."""
+    _fields_ = [("raw", C.c_ubyte * 16), ("_double", C.c_double * 2), ("_uint64", C.c_uint64 * 2)]
+
+
+class Dim3(C.Structure):
+    _fields_ = [("x", C.c_uint), ("y", C.c_uint), ("z", C.c_uint)]
+
+
+class ReduceAxisData(C.Structure):
+    _fields_ = [("size", C.c_size_t * 8), ("rsize", C.c_size_t * 8),
+                ("strides1", C.c_ssize_t * 8), ("strides2", C.c_ssize_t * 8), ("rstrides", C.c_ssize_t * 8),
+                ("ptr1", C.c_void_p), ("ptr2", C.c_void_p), ("ptrBuffer", C.c_void_p),
+                ("nelem", C.c_size_t), ("relem", C.c_size_t), ("ndims", C.c_int), ("rdims", C.c_int)]
+
+
+class ReduceAxisConfig(C.Structure):
+    _fields_ = [("data", ReduceAxisData), ("mode", C.c_int),
+                ("gridSize", Dim3), ("blockSize", Dim3), ("gridSizeFinalize", Dim3), ("blockSizeFinalize", Dim3),
+                ("bufferSize", C.c_size_t), ("sharedMem", C.c_size_t), ("sharedMemFinalize", C.c_size_t),
+                ("stream", C.c_void_p)]
+
+
+class Operand(C.Structure):
+    """solid_gpu_operand of the mixed-dtype fused entry points."""
+    _fields_ = [("ptr", C.c_void_p), ("strides", C.POINTER(C.c_ssize_t)), ("dtype", C.c_int),
+                ("byteswapped", C.c_int)]
+
+
+def _sizes(seq):
+    return (C.c_size_t * max(len(seq), 1))(*seq)
+
+
+def _strides(seq):
+    return (C.c_ssize_t * max(len(seq), 1))(*seq)
+
+
+def scalar_from_bytes(raw: bytes) -> Scalar:
+    s = Scalar()
+    C.memmove(C.addressof(s), raw, min(len(raw), 16))
+    return s
+
+
+class SolidGPU:
+    """Thin, typed access to every exported entry point."""
+
+    def __init__(self, path: Path | str = LIB_PATH):
+        path = Path(path)
+        if not path.exists():
+            raise ImportError("%s is missing: build it with ocean-tensor-package_b200/build.py "
+                              "(there is no CPU fallback)" % path)
+        self.path = path
+        self.dll = C.CDLL(str(path), mode=C.RTLD_GLOBAL)
+        self.dll.solid_gpu_initialize.restype = C.c_int
+
+    # -- helpers ---------------------------------------------------------------
+    def errmsg(self) -> str:
+        p = C.c_char_p.in_dll(self.dll, "solid_errmsg")
+        return (p.value or b"").decode(errors="replace")
+
+    def _check(self, status: int, what: str):
+        if status != 0:
+            raise SolidError("%s: %s" % (what, self.errmsg()))
+
+    def fn(self, name: str):
+        f = getattr(self.dll, name)
+        f.restype = C.c_int
+        return f
+
+    def has(self, name: str) -> bool:
+        return hasattr(self.dll, name)
+
+    def initialize(self):
+        self._check(self.dll.solid_gpu_initialize(), "solid_gpu_initialize")
+
+    # -- elementwise -------------------------------------------------------------
+    def fill(self, name, dtype, size, strides, ptr, value: bytes, stream=0):
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr),
+                      scalar_from_bytes(value), C.c_void_p(stream)), "%s_%s" % (name, dtype))
+
+    def masked_fill(self, dtype, size, strides1, ptr1, strides2, ptr2, value: bytes, stream=0):
+        f = self.fn("solid_gpu_masked_fill_%s" % dtype)
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
+                      _strides(strides2), C.c_void_p(ptr2), scalar_from_bytes(value), C.c_void_p(stream)),
+                    "masked_fill_%s" % dtype)
+
+    def unary(self, name, dtype, size, strides1, ptr1, strides2, ptr2, stream=0):
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
+                      _strides(strides2), C.c_void_p(ptr2), C.c_void_p(stream)), "%s_%s" % (name, dtype))
+
+    def binary(self, name, dtype, size, strides1, ptr1, strides2, ptr2, strides3, ptr3, stream=0):
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
+                      _strides(strides2), C.c_void_p(ptr2), _strides(strides3), C.c_void_p(ptr3),
+                      C.c_void_p(stream)), "%s_%s" % (name, dtype))
+
+    def axpy(self, dtype, size, a: bytes, strides1, ptr1, strides2, ptr2, strides3, ptr3, stream=0):
+        f = self.fn("solid_gpu_axpy_%s" % dtype)
+        self._check(f(C.c_int(len(size)), _sizes(size), scalar_from_bytes(a), _strides(strides1), C.c_void_p(ptr1),
+                      _strides(strides2), C.c_void_p(ptr2), _strides(strides3), C.c_void_p(ptr3),
+                      C.c_void_p(stream)), "axpy_%s" % dtype)
+
+    def byteswap(self, dtype, size, strides, ptr, stream=0):
+        f = self.fn("solid_gpu_byteswap_%s" % dtype)
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), C.c_void_p(stream)),
+                    "byteswap_%s" % dtype)
+
+    def copy(self, src, dst, size1, strides1, ptr1, size2, strides2, ptr2, stream=0, variant="copy"):
+        """variant: 'copy', 'byteswap_copy' (source bytes reversed) or 'copy_regular' (one shape)."""
+        f = self.fn("solid_gpu_%s_%s_%s" % (variant, src, dst))
+        if variant == "copy_regular":
+            st = f(C.c_int(len(size1)), _sizes(size1), _strides(strides1), C.c_void_p(ptr1),
+                   _strides(strides2), C.c_void_p(ptr2), C.c_void_p(stream))
+        else:
+            st = f(C.c_int(len(size1)), _sizes(size1), _strides(strides1), C.c_void_p(ptr1),
+                   C.c_int(len(size2)), _sizes(size2), _strides(strides2), C.c_void_p(ptr2), C.c_void_p(stream))
+        self._check(st, "%s_%s_%s" % (variant, src, dst))
+
+    def copy_ex(self, src, dst, flags, size1, strides1, ptr1, size2, strides2, ptr2, stream=0):
+        f = self.fn("solid_gpu_copy_ex")
+        self._check(f(C.c_int(dt.INDEX[src]), C.c_int(dt.INDEX[dst]), C.c_int(flags),
+                      C.c_int(len(size1)), _sizes(size1), _strides(strides1), C.c_void_p(ptr1),
+                      C.c_int(len(size2)), _sizes(size2), _strides(strides2), C.c_void_p(ptr2),
+                      C.c_void_p(stream)), "copy_ex %s->%s" % (src, dst))
+
+    # -- reductions ----------------------------------------------------------------
+    def reduce_all_buffer_size(self, nelem: int, device: int) -> int:
+        out = C.c_size_t(0)
+        self._check(self.fn("solid_gpu_reduce_all_buffer_size")(C.c_size_t(nelem), C.c_int(device), C.byref(out)),
+                    "reduce_all_buffer_size")
+        return out.value
+
+    def reduce_all(self, name, dtype, size, strides, ptr, buffer, stream=0, bounds=(), p=None) -> bytes:
+        """Run a global reduction; returns the 16 raw result bytes (host)."""
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        result = (C.c_ubyte * 16)()
+        args = [C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr)]
+        keep = []
+        for b in bounds:
+            s = scalar_from_bytes(b); keep.append(s); args.append(C.byref(s))
+        if p is not None:
+            args.append(C.c_double(p))
+        args += [C.cast(result, C.c_void_p), C.c_void_p(buffer), C.c_void_p(stream)]
+        self._check(f(*args), "%s_%s" % (name, dtype))
+        return bytes(result)
+
+    def reduce_all_device(self, name, dtype, size, strides, ptr, result_ptr, buffer, stream=0):
+        f = self.fn("solid_gpu_reduce_all_device")
+        self._check(f(C.c_char_p(name.encode()), C.c_int(dt.INDEX[dtype]), C.c_int(len(size)), _sizes(size),
+                      _strides(strides), C.c_void_p(ptr), C.c_void_p(result_ptr), C.c_void_p(buffer),
+                      C.c_void_p(stream)), "reduce_all_device %s %s" % (name, dtype))
+
+    def reduce_axis_prepare(self, elemsize, size, strides1, ptr1, strides2, ptr2, rsize, rstrides, stream=0):
+        cfg = ReduceAxisConfig()
+        f = self.fn("solid_gpu_reduce_axis_prepare")
+        self._check(f(C.byref(cfg), C.c_int(elemsize), C.c_int(len(size)), _sizes(size), _strides(strides1),
+                      C.c_void_p(ptr1), _strides(strides2), C.c_void_p(ptr2), C.c_int(len(rsize)), _sizes(rsize),
+                      _strides(rstrides), C.c_void_p(stream)), "reduce_axis_prepare")
+        return cfg
+
+    def reduce_axis(self, name, dtype, cfg: ReduceAxisConfig, p=None):
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        st = f(C.byref(cfg)) if p is None else f(C.byref(cfg), C.c_double(p))
+        self._check(st, "%s_%s" % (name, dtype))
+
+    # -- fused -----------------------------------------------------------------------
+    def axpy_sums_buffer_size(self, device: int) -> int:
+        out = C.c_size_t(0)
+        self._check(self.fn("solid_gpu_axpy_sums_buffer_size")(C.c_int(device), C.byref(out)), "axpy_sums_buffer_size")
+        return out.value
+
+    def axpy_sums(self, dtype, n, a: bytes, x, y, z, sums, partials, stream=0):
+        f = self.fn("solid_gpu_axpy_sums_%s" % dtype)
+        self._check(f(C.c_size_t(n), scalar_from_bytes(a), C.c_void_p(x), C.c_void_p(y), C.c_void_p(z),
+                      C.c_void_p(sums), C.c_void_p(partials), C.c_void_p(stream)), "axpy_sums_%s" % dtype)
+
+    def mixed_multiply_add(self, size, operands, ctype, stream=0):
+        """operands: four tuples (ptr, strides, dtype name, byteswapped) for a, b, c, dst."""
+        ops, keep = [], []
+        for ptr, strides, dtype, swapped in operands:
+            st = _strides(strides); keep.append(st)
+            ops.append(Operand(C.c_void_p(ptr), C.cast(st, C.POINTER(C.c_ssize_t)), dt.INDEX[dtype], int(bool(swapped))))
+        f = self.fn("solid_gpu_mixed_multiply_add")
+        self._check(f(C.c_int(len(size)), _sizes(size), C.byref(ops[0]), C.byref(ops[1]), C.byref(ops[2]),
+                      C.byref(ops[3]), C.c_int(dt.INDEX[ctype]), C.c_void_p(stream)), "mixed_multiply_add")
+
+
+_instance: SolidGPU | None = None
+
+
+def get() -> SolidGPU:
+    global _instance
+    if _instance is None:
+        _instance = SolidGPU()
+    return _instance

@@ -1,0 +1,126 @@
+"""ctypes access to the reference's Solid CPU library (oracle/_ref/libsolid_core_cpu.so).
+
+TEST INFRASTRUCTURE: the checker the CUDA path is compared with, and the timed
+CPU baseline.  The library is the unmodified reference code, built by
+oracle/build_ref.py; its entry points are declared in the reference's
+solid/src/core/cpu/solid_core_cpu.src (elementwise :106-255, copy :27-52,
+global reductions :263-332, axis reductions :341-413).  CPU signatures are the
+GPU ones without stream and scratch buffer.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "_ref" / "libsolid_core_cpu.so"
+
+
+def available() -> bool:
+    return LIB_PATH.exists()
+
+
+def _sizes(seq):
+    return (C.c_size_t * max(len(seq), 1))(*seq)
+
+
+def _strides(seq):
+    return (C.c_ssize_t * max(len(seq), 1))(*seq)
+
+
+class Scalar(C.Union):
+    _fields_ = [("raw", C.c_ubyte * 16), ("_double", C.c_double * 2)]
+
+
+def _scalar(raw: bytes) -> Scalar:
+    s = Scalar()
+    C.memmove(C.addressof(s), raw, min(len(raw), 16))
+    return s
+
+
+class SolidCPU:
+    def __init__(self, path=LIB_PATH):
+        if not Path(path).exists():
+            raise ImportError("%s is missing: run oracle/build_ref.py where the reference checkout is present" % path)
+        self.dll = C.CDLL(str(path))
+
+    def errmsg(self):
+        return (C.c_char_p.in_dll(self.dll, "solid_errmsg").value or b"").decode(errors="replace")
+
+    def _check(self, st, what):
+        if st != 0:
+            raise RuntimeError("%s: %s" % (what, self.errmsg()))
+
+    def fn(self, name):
+        f = getattr(self.dll, name)
+        f.restype = C.c_int
+        return f
+
+    def has(self, name):
+        return hasattr(self.dll, name)
+
+    def set_threads(self, n: int):
+        """OpenMP threads used by the reference (its float reduction order depends on it)."""
+        import os
+        os.environ["OMP_NUM_THREADS"] = str(n)
+        try:
+            C.CDLL("libgomp.so.1").omp_set_num_threads(C.c_int(n))
+        except OSError:
+            pass
+
+    def fill(self, name, dtype, size, strides, ptr, value: bytes):
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(
+            C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), _scalar(value)), name)
+
+    def masked_fill(self, dtype, size, strides1, ptr1, strides2, ptr2, value: bytes):
+        self._check(self.fn("solid_cpu_masked_fill_%s" % dtype)(
+            C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1), _strides(strides2),
+            C.c_void_p(ptr2), _scalar(value)), "masked_fill")
+
+    def unary(self, name, dtype, size, strides1, ptr1, strides2, ptr2):
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(
+            C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
+            _strides(strides2), C.c_void_p(ptr2)), name)
+
+    def binary(self, name, dtype, size, strides1, ptr1, strides2, ptr2, strides3, ptr3):
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(
+            C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
+            _strides(strides2), C.c_void_p(ptr2), _strides(strides3), C.c_void_p(ptr3)), name)
+
+    def byteswap(self, dtype, size, strides, ptr):
+        self._check(self.fn("solid_cpu_byteswap_%s" % dtype)(
+            C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr)), "byteswap")
+
+    def copy(self, src, dst, size1, strides1, ptr1, size2, strides2, ptr2, variant="copy"):
+        self._check(self.fn("solid_cpu_%s_%s_%s" % (variant, src, dst))(
+            C.c_int(len(size1)), _sizes(size1), _strides(strides1), C.c_void_p(ptr1),
+            C.c_int(len(size2)), _sizes(size2), _strides(strides2), C.c_void_p(ptr2)), variant)
+
+    def reduce_all(self, name, dtype, size, strides, ptr, bounds=(), p=None) -> bytes:
+        result = (C.c_ubyte * 16)()
+        args = [C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr)]
+        keep = []
+        for b in bounds:
+            s = _scalar(b); keep.append(s); args.append(C.byref(s))
+        if p is not None:
+            args.append(C.c_double(p))
+        args.append(C.cast(result, C.c_void_p))
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(*args), name)
+        return bytes(result)
+
+    def reduce_axis(self, name, dtype, size, strides1, ptr1, strides2, ptr2, rsize, rstrides, p=None):
+        args = [C.c_int(len(size)), _sizes(size)]
+        if p is not None:
+            args.append(C.c_double(p))
+        args += [_strides(strides1), C.c_void_p(ptr1), _strides(strides2), C.c_void_p(ptr2),
+                 C.c_int(len(rsize)), _sizes(rsize), _strides(rstrides)]
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(*args), name)
+
+
+_instance = None
+
+
+def get() -> SolidCPU:
+    global _instance
+    if _instance is None:
+        _instance = SolidCPU()
+    return _instance

@@ -1,0 +1,214 @@
+"""Parity of the elementwise entry points (unary, binary, fill) with the reference's
+Solid CPU library on the same seeded buffers, through the C-ABI, over contiguous,
+offset, padded, transposed, broadcast, reversed, scalar and in-place layouts.
+
+Tolerances: bit-exact for bool/integer results and for IEEE operations (add,
+subtract, multiply, divide, sqrt, min/max, rounding, sign, conj, ...); at most
+2 ulp for the transcendental functions named by the benchmark configurations
+(exp, log, sin and relatives on real types) and 8 ulp for the remaining
+library functions, whose GPU and glibc implementations are different programs.
+"""
+import zlib
+
+import numpy as np
+import pytest
+
+import util
+from solid_b200 import dtypes as dt
+from solid_b200 import oplist as ol
+
+pytestmark = pytest.mark.gpu
+
+EXACT_UNARY = {"negative", "conj", "reciprocal", "bitwise_not", "logical_not", "sqrt", "square", "fabs", "sign",
+               "ceil", "floor", "trunc", "round", "isinf", "isnan", "isfinite", "isposinf", "isneginf", "absolute"}
+ULP2_UNARY = {"sin", "cos", "exp", "log", "exp2", "log2", "log10", "expm1", "log1p", "arctan", "tanh", "cbrt"}
+DOMAIN = {"arcsin": "unit", "arccos": "unit", "arctanh": "unit", "arccosh": "positive",
+          "log": "positive", "log2": "positive", "log10": "positive", "log1p": "positive", "sqrt": "positive"}
+
+
+def unary_tolerance(op, dtype):
+    if dtype in dt.GROUPS["integer_bool"]:
+        return 0 if op in EXACT_UNARY else 1          # integer results of double-precision library functions
+    if dtype in dt.COMPLEX:
+        if op in {"negative", "conj", "square", "ceil", "floor", "trunc", "round", "isinf", "isnan", "isfinite"}:
+            return 0
+        return 16                                      # compositions of several library functions
+    if op in EXACT_UNARY:
+        return 0
+    return 2 if op in ULP2_UNARY else 8
+
+
+def layouts(dtype, out_dtype=None):
+    """(name, size, view of operand 1, view of result) cases."""
+    od = out_dtype or dtype
+    es, eo = dt.SIZE[dtype], dt.SIZE[od]
+    cases = []
+    for n in (0, 1, 7, 1000, 4099):
+        cases.append(("contig%d" % n, [n], util.dense_view(dtype, [n]), util.dense_view(od, [n])))
+    cases.append(("offset", [1003], util.dense_view(dtype, [1003], offset_elems=1), util.dense_view(od, [1003], offset_elems=3)))
+    cases.append(("padded", [32, 9], util.dense_view(dtype, [32, 9], pad_elems=16), util.dense_view(od, [32, 9], pad_elems=16)))
+    cases.append(("padded_odd", [13, 7], util.dense_view(dtype, [13, 7], pad_elems=3), util.dense_view(od, [13, 7])))
+    v = util.dense_view(dtype, [11, 37]); vt = util.View(dtype, [37, 11], [v.strides[1], v.strides[0]], 0, v.nbytes)
+    cases.append(("transposed", [37, 11], vt, util.dense_view(od, [37, 11])))
+    vb = util.View(dtype, [40, 6], [0, es], 0, 6 * es + 64)
+    cases.append(("row_broadcast", [40, 6], vb, util.dense_view(od, [40, 6])))
+    vs = util.View(dtype, [50, 3], [0, 0], 0, 64)
+    cases.append(("scalar_broadcast", [50, 3], vs, util.dense_view(od, [50, 3])))
+    v3 = util.dense_view(dtype, [5, 6, 7])
+    vr = util.View(dtype, [5, 6, 7], [v3.strides[0], -v3.strides[1], v3.strides[2]], 5 * v3.strides[1], v3.nbytes)
+    cases.append(("reversed_dim", [5, 6, 7], vr, util.dense_view(od, [5, 6, 7])))
+    cases.append(("zero_dim", [], util.dense_view(dtype, []), util.dense_view(od, [])))
+    return cases
+
+
+def out_type_unary(op, dtype):
+    if op in ("isinf", "isnan", "isfinite", "isposinf", "isneginf"):
+        return "bool"
+    if op == "absolute":
+        return dt.elem_type(dtype)
+    return dtype
+
+
+@pytest.mark.parametrize("op", sorted(ol.UNARY_OPS))
+def test_unary_matches_reference(op, gpu, cpu):
+    dev = util.Device()
+    for dtype in dt.GROUPS[ol.UNARY_OPS[op]]:
+        if op == "arctanh" and dtype in dt.COMPLEX:
+            continue          # the reference never writes the real part (unary_ops.h:472-474)
+        od = out_type_unary(op, dtype)
+        kind = DOMAIN.get(op, "special" if op in EXACT_UNARY else "general")
+        if dtype in dt.GROUPS["integer_bool"] and op not in EXACT_UNARY:
+            kind = "small" if op in ("exp", "exp2", "exp10", "expm1", "sinh", "cosh") else kind
+            if op in ("exp10",):
+                kind = "unit"
+        rng = np.random.default_rng(zlib.crc32(("%s %s" % (op, dtype)).encode()))
+        for name, size, vin, vout in layouts(dtype, od):
+            src = util.fill_buffer(vin, rng, kind)
+            dst0 = util.fill_buffer(vout, rng, "general")
+            want = dst0.copy()
+            cpu.unary(op, dtype, size, vin.strides, src.ctypes.data + vin.offset, vout.strides, want.ctypes.data + vout.offset)
+            dsrc, ddst = dev.upload(src), dev.upload(dst0)
+            gpu.unary(op, dtype, size, vin.strides, dsrc.data_ptr() + vin.offset, vout.strides,
+                      ddst.data_ptr() + vout.offset, dev.stream)
+            got = dev.download(ddst)
+            what = "%s_%s %s" % (op, dtype, name)
+            # bytes outside the view must be untouched; inside compare with the op's tolerance
+            g, w = util.gather(got, vout), util.gather(want, vout)
+            util.assert_same(g, w, od, unary_tolerance(op, dtype), what)
+            mask = np.ones(len(got), dtype=bool)
+            if vout.nelem:
+                idx = np.zeros(1, dtype=np.int64)
+                for s, st in zip(vout.size, vout.strides):
+                    idx = (np.arange(s, dtype=np.int64)[:, None] * st + idx[None, :]).reshape(-1)
+                mask[(idx[:, None] + vout.offset + np.arange(dt.SIZE[od])[None, :]).reshape(-1)] = False
+            assert np.array_equal(got[mask], dst0[mask]), what + ": wrote outside the destination view"
+
+
+def test_unary_in_place(gpu, cpu):
+    dev = util.Device()
+    rng = np.random.default_rng(5)
+    for dtype, op in (("float", "sqrt"), ("int32", "negative"), ("cdouble", "conj"), ("half", "square")):
+        v = util.dense_view(dtype, [777])
+        src = util.fill_buffer(v, rng, "positive")
+        want = src.copy()
+        cpu.unary(op, dtype, v.size, v.strides, want.ctypes.data, v.strides, want.ctypes.data)
+        d = dev.upload(src)
+        gpu.unary(op, dtype, v.size, v.strides, d.data_ptr(), v.strides, d.data_ptr(), dev.stream)
+        util.assert_same(util.gather(dev.download(d), v), util.gather(want, v), dtype, 0, "%s in place" % op)
+
+
+# ---------------------------------------------------------------------------
+EXACT_BINARY = set(ol.BINARY_OPS) - {"power", "fmod"}
+
+
+def second_type(op, dtype):
+    if op in ("bitshift_left", "bitshift_right"):
+        return "int8"
+    if op == "power" and dtype in dt.GROUPS["integer_bool"]:
+        return "int16"
+    return dtype
+
+
+def out_type_binary(op, dtype):
+    return "bool" if op in ol.COMPARE_OPS else dtype
+
+
+def second_values(op, dtype, n, rng):
+    if op in ("bitshift_left", "bitshift_right"):
+        return rng.integers(-3, min(8, 8 * dt.SIZE[dtype]), n).astype(np.int8)
+    if op == "power" and dtype in dt.GROUPS["integer_bool"]:
+        return rng.integers(-2, 5, n).astype(np.int16)
+    return None
+
+
+@pytest.mark.parametrize("op", sorted(ol.BINARY_OPS))
+def test_binary_matches_reference(op, gpu, cpu):
+    dev = util.Device()
+    for dtype in dt.GROUPS[ol.BINARY_OPS[op]]:
+        t2, od = second_type(op, dtype), out_type_binary(op, dtype)
+        rng = np.random.default_rng(zlib.crc32(("%s %s b" % (op, dtype)).encode()))
+        kind = "special" if (op in EXACT_BINARY and dtype in dt.GROUPS["float"]) else "general"
+        if dtype in dt.GROUPS["integer"] and op in ("multiply", "power"):
+            kind = "small"
+        tol = 0
+        if op == "power" and dtype in dt.GROUPS["float"]:
+            tol, kind = 64, "positive"                     # single-precision pow inside (see mathfn.cuh)
+        if op == "fmod" and dtype in dt.REAL:
+            tol = 0
+        if dtype in dt.COMPLEX and op in ("divide", "true_divide"):
+            tol = 0
+        base_cases = layouts(dtype, od)
+        for i, (name, size, v1, vout) in enumerate(base_cases):
+            # second operand: dense, or a broadcast row/scalar for some cases
+            if name == "padded":
+                v2 = util.View(t2, size, [0, dt.SIZE[t2]], 0, size[1] * dt.SIZE[t2] + 64)
+            elif name == "contig1000":
+                v2 = util.View(t2, size, [0], 0, 64)
+            else:
+                v2 = util.dense_view(t2, size)
+            a = util.fill_buffer(v1, rng, kind)
+            b = util.fill_buffer(v2, rng, kind)
+            sv = second_values(op, dtype, v2.nbytes // dt.SIZE[t2], rng)
+            if sv is not None:
+                b = np.zeros(v2.nbytes, dtype=np.uint8); raw = sv.view(np.uint8); b[: len(raw)] = raw[: len(b)]
+            dst0 = util.fill_buffer(vout, rng, "general")
+            want = dst0.copy()
+            cpu.binary(op, dtype, size, v1.strides, a.ctypes.data + v1.offset, v2.strides, b.ctypes.data + v2.offset,
+                       vout.strides, want.ctypes.data + vout.offset)
+            da, db, dd = dev.upload(a), dev.upload(b), dev.upload(dst0)
+            gpu.binary(op, dtype, size, v1.strides, da.data_ptr() + v1.offset, v2.strides, db.data_ptr() + v2.offset,
+                       vout.strides, dd.data_ptr() + vout.offset, dev.stream)
+            got = dev.download(dd)
+            util.assert_same(util.gather(got, vout), util.gather(want, vout), od, tol, "%s_%s %s" % (op, dtype, name))
+
+
+@pytest.mark.parametrize("dtype", dt.NAMES)
+def test_fill_and_masked_fill(dtype, gpu, cpu):
+    dev = util.Device()
+    rng = np.random.default_rng(dt.INDEX[dtype])
+    value = util.random_values(dtype, 1, rng).tobytes()
+    for name, size, v, _ in layouts(dtype):
+        if name in ("row_broadcast", "scalar_broadcast"):
+            continue                                     # a destination cannot be a broadcast view
+        buf = util.fill_buffer(v, rng)
+        want = buf.copy()
+        cpu.fill("fill", dtype, size, v.strides, want.ctypes.data + v.offset, value)
+        d = dev.upload(buf)
+        gpu.fill("fill", dtype, size, v.strides, d.data_ptr() + v.offset, value, dev.stream)
+        assert np.array_equal(dev.download(d), want), "fill_%s %s" % (dtype, name)
+        # masked fill
+        vm = util.dense_view("bool", size)
+        mask = util.fill_buffer(vm, rng)
+        want = buf.copy()
+        cpu.masked_fill(dtype, size, v.strides, want.ctypes.data + v.offset, vm.strides, mask.ctypes.data, value)
+        d, dm = dev.upload(buf), dev.upload(mask)
+        gpu.masked_fill(dtype, size, v.strides, d.data_ptr() + v.offset, vm.strides, dm.data_ptr(), value, dev.stream)
+        assert np.array_equal(dev.download(d), want), "masked_fill_%s %s" % (dtype, name)
+    if dtype in dt.GROUPS["float"]:
+        v = util.dense_view(dtype, [999])
+        buf = util.fill_buffer(v, rng, "special")
+        want = buf.copy()
+        cpu.fill("fill_nan", dtype, v.size, v.strides, want.ctypes.data, value)
+        d = dev.upload(buf)
+        gpu.fill("fill_nan", dtype, v.size, v.strides, d.data_ptr(), value, dev.stream)
+        assert np.array_equal(dev.download(d), want), "fill_nan_%s" % dtype
