@@ -35,6 +35,7 @@ SINGLE_UNITS = ["base", "luts", "reduce_plan", "fused"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--fmad=false",            # one rounding per operation, as the CPU oracle computes
+              "-Xfatbin", "-compress-all",
               "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
               "-I%s" % INCLUDE, "-I%s" % CSRC]
 

@@ -38,8 +38,16 @@ template <class W> SD_D W m_exp10(W x) { return m_exp<W>(m_ln10<W>() * x); }
 
 template <class W> SD_D W m_atan2(W y, W x)
 {  if constexpr (std::is_same<W, float>::value) return atan2f(y, x); else return ::atan2(y, x); }
+// Single precision hypot goes through double (products exact, one rounding in the
+// sum, one in the root, one in the narrowing), which is how current glibc
+// evaluates hypotf; the double version is the CUDA library function.
 template <class W> SD_D W m_hypot(W x, W y)
-{  if constexpr (std::is_same<W, float>::value) return hypotf(x, y); else return ::hypot(x, y); }
+{
+   if constexpr (std::is_same<W, float>::value) {
+      if (fabsf(x) == (float)(1. / 0.) || fabsf(y) == (float)(1. / 0.)) return (float)(1. / 0.);
+      return (float)::sqrt((double)x * (double)x + (double)y * (double)y);
+   } else return ::hypot(x, y);
+}
 template <class W> SD_D W m_fmod(W x, W y)
 {  if constexpr (std::is_same<W, float>::value) return fmodf(x, y); else return ::fmod(x, y); }
 template <class W> SD_D W m_copysign(W x, W y)

@@ -19,9 +19,13 @@ class SolidError(RuntimeError):
     """A Solid entry point returned -1; the message is the library's solid_errmsg."""
 
 
-class Scalar(C.Union):
-    """solid_scalar (solid/include/solid/base/generic/scalar.h:27-43): 16 bytes."""
-    _fields_ = [("raw", C.c_ubyte * 16), ("_double", C.c_double * 2), ("_uint64", C.c_uint64 * 2)]
+class Scalar(C.Structure):
+    """solid_scalar passed BY VALUE (solid/include/solid/base/generic/scalar.h:27-43): a 16-byte union.
+    The x86-64 calling convention classifies its first eight bytes as INTEGER (the integer members
+    overlap the floating ones there) and its second eight bytes as SSE (only cdouble.imag lives
+    there), so it travels in one general and one vector register.  ctypes cannot pass unions by
+    value; a struct {uint64, double} has exactly that classification."""
+    _fields_ = [("lo", C.c_uint64), ("hi", C.c_double)]
 
 
 class Dim3(C.Structure):

@@ -27,8 +27,10 @@ def _strides(seq):
     return (C.c_ssize_t * max(len(seq), 1))(*seq)
 
 
-class Scalar(C.Union):
-    _fields_ = [("raw", C.c_ubyte * 16), ("_double", C.c_double * 2)]
+class Scalar(C.Structure):
+    """solid_scalar by value: first eightbyte INTEGER class, second SSE (see the x86-64 ABI);
+    ctypes cannot pass the union itself by value."""
+    _fields_ = [("lo", C.c_uint64), ("hi", C.c_double)]
 
 
 def _scalar(raw: bytes) -> Scalar:

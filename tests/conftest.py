@@ -34,4 +34,9 @@ def cpu():
     if not ref.available():
         pytest.skip("oracle/_ref/libsolid_core_cpu.so not built")
     c = ref.get()
+    # One OpenMP thread: the reference's cooperative multi-thread axis reduction (omp2 mode of
+    # solid/include/solid/core/cpu/reduce_axis.h:456-640) mis-steps when a thread's share of a
+    # multi-dimensional reduced range starts inside a row (ridx[0] is never reset, line 574), so
+    # its results there depend on the thread count; the sequential path is the well-defined oracle.
+    c.set_threads(1)
     return c
