@@ -11,6 +11,7 @@
 #include <cstddef>
 #include <type_traits>
 #include <cuda_runtime.h>
+#include <cuda_fp16.h>
 
 namespace sd {
 
@@ -74,6 +75,15 @@ template <class T> using ework_t = work_t<elem_t<T>>;              // its work t
 // magnitude for zero after the sign was stripped and returns a literal 0).
 SD_HD float half_to_float(Half hh)
 {
+#ifdef __CUDA_ARCH__
+   // the hardware conversion is exact for zero, subnormal and normal inputs; only the
+   // two deviations of half.c are patched in: +-0 -> +0, and inf/nan rebuilt from the bits
+   const uint32_t h = hh.v;
+   float f = __half2float(__ushort_as_half(hh.v));
+   if ((h & 0x7C00u) == 0x7C00u) f = __uint_as_float(((h & 0x8000u) << 16) | 0x7F800000u | ((h & 0x03FFu) << 13));
+   if ((h & 0x7FFFu) == 0) f = 0.0f;
+   return f;
+#else
    uint32_t h = hh.v;
    uint32_t s = (h & 0x8000u) << 16;
    h &= 0x7FFFu;
@@ -89,9 +99,6 @@ SD_HD float half_to_float(Half hh)
       d = (h << 13) + 0x38000000u;
    }
    d |= s;
-#ifdef __CUDA_ARCH__
-   return __uint_as_float(d);
-#else
    float f; __builtin_memcpy(&f, &d, 4); return f;
 #endif
 }
@@ -110,21 +117,15 @@ SD_HD Half float_to_half(float f)
 #else
    __builtin_memcpy(&raw, &f, 4);
 #endif
-   uint32_t d = raw & 0x007FFFFFu;
-   uint32_t e = (raw >> 16) & 0x7FFFu;
-   uint16_t s = (uint16_t)((raw >> 16) & 0x8000u);
-   e >>= 7;
-   Half r;
-   if (e < 112u) { r.v = 0; return r; }
-   if (e > 143u) {
-      if (e == 255u && d != 0) r.v = 0x7F00; else r.v = (uint16_t)(s | 0x7C00u);
-      return r;
-   }
-   uint16_t x = (uint16_t)((e - 112u) << 10);
-   x |= (uint16_t)(d >> 13);
-   x |= s;
-   if ((d & 0x1FFFu) >= 0x1000u) x++;
-   r.v = x;
+   const uint32_t d = raw & 0x007FFFFFu;
+   const uint32_t e = (raw >> 23) & 0xFFu;
+   const uint32_t s = (raw >> 16) & 0x8000u;
+   // branch free: the regular encoding (16-bit wrap-around included), then the two overrides
+   uint32_t x = ((((e - 112u) << 10) | (d >> 13) | s) + ((d & 0x1FFFu) >= 0x1000u ? 1u : 0u)) & 0xFFFFu;
+   const uint32_t special = (e == 255u && d != 0) ? 0x7F00u : (s | 0x7C00u);
+   x = (e > 143u) ? special : x;
+   x = (e < 112u) ? 0u : x;
+   Half r; r.v = (uint16_t)x;
    return r;
 }
 

@@ -67,11 +67,54 @@ template <class A> struct ew_traits {
 // family accepts such tensors).  Loads fetch the aligned 32-bit words that cover
 // the bytes and realign them with a funnel shift; the word after the last one is
 // touched only when the data really extends into it.  Stores go byte by byte.
+template <int NW> SD_D void ld_words_aligned16(const uint4 *q, uint32_t (&w)[NW])
+{
+#pragma unroll
+   for (int i = 0; i < NW / 4; i++) {
+      uint4 r = __ldg(q + i);
+      w[4 * i] = r.x; w[4 * i + 1] = r.y; w[4 * i + 2] = r.z; w[4 * i + 3] = r.w;
+   }
+}
 template <class T, int N> SD_D Vec<T, N> ld_unaligned(const char *p)
 {
    constexpr int B = (int)sizeof(T) * N;
    Vec<T, N> o;
-   if constexpr (B % 4 == 0) {
+   if constexpr (B % 16 == 0) {
+      // B bytes starting anywhere: fetch the B + 16 bytes of the enclosing 16-byte lines with
+      // 128-bit loads (the extra line is the next thread's first one, so it comes from cache),
+      // then realign.  The word offset 0..3 is the same for every thread of a contiguous copy,
+      // so the switch does not diverge.
+      const uintptr_t a = reinterpret_cast<uintptr_t>(p);
+      const uint4 *q = reinterpret_cast<const uint4 *>(a & ~(uintptr_t)15);
+      const uint32_t wo = (uint32_t)(a & 15) >> 2, sh = (uint32_t)(a & 3) * 8;
+      constexpr int NW = B / 4;
+      uint32_t w[NW + 4];
+      if ((a & 15) == 0) { uint32_t t[NW]; ld_words_aligned16<NW>(q, t);
+#pragma unroll
+         for (int i = 0; i < NW; i++) w[i] = t[i];
+         w[NW] = w[NW + 1] = w[NW + 2] = w[NW + 3] = 0; }
+      else ld_words_aligned16<NW + 4>(q, w);
+      uint32_t r[NW];
+      switch (wo) {
+         case 0:
+#pragma unroll
+            for (int i = 0; i < NW; i++) r[i] = __funnelshift_r(w[i], w[i + 1], sh);
+            break;
+         case 1:
+#pragma unroll
+            for (int i = 0; i < NW; i++) r[i] = __funnelshift_r(w[i + 1], w[i + 2], sh);
+            break;
+         case 2:
+#pragma unroll
+            for (int i = 0; i < NW; i++) r[i] = __funnelshift_r(w[i + 2], w[i + 3], sh);
+            break;
+         default:
+#pragma unroll
+            for (int i = 0; i < NW; i++) r[i] = __funnelshift_r(w[i + 3], (i + 4 < NW + 4) ? w[i + 4] : 0u, sh);
+            break;
+      }
+      memcpy(&o, r, B);
+   } else if constexpr (B % 4 == 0) {
       const uintptr_t a = reinterpret_cast<uintptr_t>(p);
       const uint32_t *q = reinterpret_cast<const uint32_t *>(a & ~(uintptr_t)3);
       const uint32_t sh = (uint32_t)(a & 3) * 8;

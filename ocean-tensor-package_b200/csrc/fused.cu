@@ -128,6 +128,7 @@ struct MixParams {
    int      dtype[4];
    int      swap[4];
    int      unal[4];
+   int      comp[4];            // bytes of one real component
    int64_t  stride[4][MAXD];
    int64_t  size[MAXD];
    int      ndims;
@@ -137,53 +138,51 @@ struct MixParams {
    uint64_t tiles0, tilest;
 };
 
-// Load `es` raw bytes (possibly unaligned) into the low bytes of a 16-byte buffer.
-template <int ES> SD_D void load_raw(const char *p, bool unal, void *out)
+// Operand access is split in two so that a thread can issue many loads before it
+// consumes any: load_bits fetches the raw bytes of one real component (complex
+// operands contribute their real part only), bits_as converts them to the compute
+// type.  Both switch on values that are uniform over the launch.
+SD_D uint64_t load_bits(const char *p, int comp_size, bool unal)
 {
-   using raw = typename raw_of<ES>::type;
-   raw r;
-   if (!unal) r = ld_one<raw>(p);
-   else { uint8_t b[ES];
-#pragma unroll
-      for (int i = 0; i < ES; i++) b[i] = __ldg(reinterpret_cast<const uint8_t *>(p) + i);
-      memcpy(&r, b, ES); }
-   memcpy(out, &r, ES);
-}
-template <class S> SD_D S load_typed(const char *p, bool swap, bool unal)
-{
-   S x;
-   if constexpr (is_cplx<S>) {
-      using E = elem_t<S>;
-      load_raw<sizeof(E)>(p, unal, &x.re);                 // only the real part is needed
-      if constexpr (is_half<E>) x.im.v = 0; else x.im = 0;
-      if (swap) x.re = bswap_real(x.re);
-   } else {
-      load_raw<sizeof(S)>(p, unal, &x);
-      if (swap) x = bswap<S>(x);
+   if (unal) {
+      uint64_t r = 0;
+      for (int i = 0; i < comp_size; i++) r |= (uint64_t)__ldg(reinterpret_cast<const uint8_t *>(p) + i) << (8 * i);
+      return r;
    }
+   switch (comp_size) {
+      case 1:  return ld_one<uint8_t>(p);
+      case 2:  return ld_one<uint16_t>(p);
+      case 4:  return ld_one<uint32_t>(p);
+      default: return ld_one<uint64_t>(p);
+   }
+}
+template <class S> SD_D S bits_typed(uint64_t raw, bool swap)
+{
+   typename raw_of<sizeof(S)>::type u = (typename raw_of<sizeof(S)>::type)raw;
+   S x; memcpy(&x, &u, sizeof(S));
+   if (swap) x = bswap_real(x);
    return x;
 }
-// Read one element of runtime type `dtype` as compute type C (real part of complex).
-template <class C> SD_D C load_as(const char *p, int dtype, bool swap, bool unal)
+// Raw component bits of runtime type `dtype` as compute type C.
+template <class C> SD_D C bits_as(uint64_t raw, int dtype, bool swap)
 {
    switch (dtype) {
-      case 0:  return convert<C>(load_typed<Bool>(p, swap, unal));
-      case 1:  return convert<C>(load_typed<uint8_t>(p, swap, unal));
-      case 2:  return convert<C>(load_typed<uint16_t>(p, swap, unal));
-      case 3:  return convert<C>(load_typed<uint32_t>(p, swap, unal));
-      case 4:  return convert<C>(load_typed<uint64_t>(p, swap, unal));
-      case 5:  return convert<C>(load_typed<int8_t>(p, swap, unal));
-      case 6:  return convert<C>(load_typed<int16_t>(p, swap, unal));
-      case 7:  return convert<C>(load_typed<int32_t>(p, swap, unal));
-      case 8:  return convert<C>(load_typed<int64_t>(p, swap, unal));
-      case 9:  return convert<C>(load_typed<Half>(p, swap, unal));
-      case 10: return convert<C>(load_typed<float>(p, swap, unal));
-      case 11: return convert<C>(load_typed<double>(p, swap, unal));
-      case 12: return convert<C>(load_typed<CHalf>(p, swap, unal));
-      case 13: return convert<C>(load_typed<CFloat>(p, swap, unal));
-      default: return convert<C>(load_typed<CDouble>(p, swap, unal));
+      case 0:  return convert<C>(bits_typed<Bool>(raw, swap));
+      case 1:  return convert<C>(bits_typed<uint8_t>(raw, swap));
+      case 2:  return convert<C>(bits_typed<uint16_t>(raw, swap));
+      case 3:  return convert<C>(bits_typed<uint32_t>(raw, swap));
+      case 4:  return convert<C>(bits_typed<uint64_t>(raw, swap));
+      case 5:  return convert<C>(bits_typed<int8_t>(raw, swap));
+      case 6:  return convert<C>(bits_typed<int16_t>(raw, swap));
+      case 7:  return convert<C>(bits_typed<int32_t>(raw, swap));
+      case 8:  return convert<C>(bits_typed<int64_t>(raw, swap));
+      case 9:  case 12: return convert<C>(bits_typed<Half>(raw, swap));
+      case 10: case 13: return convert<C>(bits_typed<float>(raw, swap));
+      default: return convert<C>(bits_typed<double>(raw, swap));
    }
 }
+template <class C> SD_D C load_as(const char *p, int dtype, int comp_size, bool swap, bool unal)
+{  return bits_as<C>(load_bits(p, comp_size, unal), dtype, swap); }
 template <class D, class C> SD_D void store_typed(char *p, C v, bool swap, bool unal)
 {
    D y = convert<D>(v);
@@ -229,28 +228,36 @@ __global__ void __launch_bounds__(256) mix_linear(const MixParams p)
       }
 #pragma unroll
       for (int k = 0; k < 4; k++) off[k] += (int64_t)r * p.stride[k][p.ndims - 1];
-      C a = load_as<C>(p.ptr[0] + off[0], p.dtype[0], p.swap[0], p.unal[0]);
-      C b = load_as<C>(p.ptr[1] + off[1], p.dtype[1], p.swap[1], p.unal[1]);
-      C c = load_as<C>(p.ptr[2] + off[2], p.dtype[2], p.swap[2], p.unal[2]);
+      uint64_t ra = load_bits(p.ptr[0] + off[0], p.comp[0], p.unal[0]);
+      uint64_t rb = load_bits(p.ptr[1] + off[1], p.comp[1], p.unal[1]);
+      uint64_t rc = load_bits(p.ptr[2] + off[2], p.comp[2], p.unal[2]);
+      C a = bits_as<C>(ra, p.dtype[0], p.swap[0]);
+      C b = bits_as<C>(rb, p.dtype[1], p.swap[1]);
+      C c = bits_as<C>(rc, p.dtype[2], p.swap[2]);
       C prod = a * b;
       C sum = prod + c;
       store_as<C>(p.ptr[3] + off[3], p.dtype[3], sum, p.swap[3], p.unal[3]);
    }
 }
 
-// Tiled variant: a 32 x 32 tile over (dimension 0, dimension dt).  Operands that
-// are dense along dt are first read with lanes running along dt (coalesced),
-// converted and parked in shared memory; then lanes run along dimension 0, the
-// remaining operands are read directly (coalesced) and the result is stored.
+// Tiled variant: a 64 x 64 tile over (dimension 0, dimension dt), 256 threads, 16 elements
+// per thread and operand.  Operands that are dense along dt are first read with lanes
+// running along dt (coalesced), converted and parked in shared memory; then lanes run
+// along dimension 0, the remaining operands are read directly (coalesced) and the result
+// is stored.  In both phases a thread issues all of its loads before it consumes any of
+// them, so sixteen independent requests per operand are in flight per thread.
+constexpr int MT = 64;                      // tile edge
+constexpr int MR = 16;                      // elements per thread (MT * MT / 256)
+
 template <class C>
 __global__ void __launch_bounds__(256) mix_tiled(const MixParams p)
 {
-   __shared__ C tile[3][32][33];
-   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;         // 32 x 8
+   extern __shared__ __align__(16) unsigned char mix_smem[];
+   C (*tile)[MT][MT + 1] = reinterpret_cast<C (*)[MT][MT + 1]>(mix_smem);
+   const int tx = threadIdx.x & (MT - 1), ty = threadIdx.x / MT;      // 64 x 4
    uint64_t bid = blockIdx.x;
    const uint64_t t0 = bid % p.tiles0; bid /= p.tiles0;
    const uint64_t tt = bid % p.tilest; bid /= p.tilest;
-   // remaining dimensions
    int64_t off[4] = {0, 0, 0, 0};
    for (int d = 1; d < p.ndims; d++) {
       if (d == p.dt) continue;
@@ -258,38 +265,59 @@ __global__ void __launch_bounds__(256) mix_tiled(const MixParams p)
 #pragma unroll
       for (int k = 0; k < 4; k++) off[k] += (int64_t)c * p.stride[k][d];
    }
-   const int64_t i0 = (int64_t)t0 * 32, it = (int64_t)tt * 32;
+   const int64_t i0 = (int64_t)t0 * MT, it = (int64_t)tt * MT;
    const int64_t n0 = p.size[0], nt = p.size[p.dt];
 
-   // phase 1: lanes along dt
+   // phase 1: lanes along dt; tile slot of operand k is the number of staged operands below k
+   int slot = 0;
 #pragma unroll
    for (int k = 0; k < 3; k++) {
       if (!(p.staged & (1u << k))) continue;
+      uint64_t raw[MR];
+      const char *base = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt];
 #pragma unroll
-      for (int j = 0; j < 4; j++) {
-         int64_t a0 = i0 + ty + 8 * j, at = it + tx;
-         if (a0 < n0 && at < nt)
-            tile[k][ty + 8 * j][tx] = load_as<C>(p.ptr[k] + off[k] + a0 * p.stride[k][0] + at * p.stride[k][p.dt],
-                                                  p.dtype[k], p.swap[k], p.unal[k]);
+      for (int j = 0; j < MR; j++) {
+         int64_t a0 = i0 + ty + 4 * j;
+         raw[j] = (a0 < n0 && it + tx < nt) ? load_bits(base + a0 * p.stride[k][0], p.comp[k], p.unal[k]) : 0;
       }
+#pragma unroll
+      for (int j = 0; j < MR; j++) tile[slot][ty + 4 * j][tx] = bits_as<C>(raw[j], p.dtype[k], p.swap[k]);
+      slot++;
    }
    __syncthreads();
    // phase 2: lanes along dimension 0
+   uint64_t raw[3][MR];
 #pragma unroll
-   for (int j = 0; j < 4; j++) {
-      int64_t a0 = i0 + tx, at = it + ty + 8 * j;
-      if (a0 < n0 && at < nt) {
-         C v[3];
+   for (int k = 0; k < 3; k++) {
+      if (p.staged & (1u << k)) continue;
+      const char *base = p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0];
 #pragma unroll
-         for (int k = 0; k < 3; k++) {
-            if (p.staged & (1u << k)) v[k] = tile[k][tx][ty + 8 * j];
-            else v[k] = load_as<C>(p.ptr[k] + off[k] + a0 * p.stride[k][0] + at * p.stride[k][p.dt],
-                                   p.dtype[k], p.swap[k], p.unal[k]);
-         }
-         C prod = v[0] * v[1];
-         C sum = prod + v[2];
-         store_as<C>(p.ptr[3] + off[3] + a0 * p.stride[3][0] + at * p.stride[3][p.dt], p.dtype[3], sum,
-                     p.swap[3], p.unal[3]);
+      for (int j = 0; j < MR; j++) {
+         int64_t at = it + ty + 4 * j;
+         raw[k][j] = (i0 + tx < n0 && at < nt) ? load_bits(base + at * p.stride[k][p.dt], p.comp[k], p.unal[k]) : 0;
+      }
+   }
+   C v[3][MR];
+   slot = 0;
+#pragma unroll
+   for (int k = 0; k < 3; k++) {
+      if (p.staged & (1u << k)) {
+#pragma unroll
+         for (int j = 0; j < MR; j++) v[k][j] = tile[slot][tx][ty + 4 * j];
+         slot++;
+      } else {
+#pragma unroll
+         for (int j = 0; j < MR; j++) v[k][j] = bits_as<C>(raw[k][j], p.dtype[k], p.swap[k]);
+      }
+   }
+   char *obase = p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0];
+#pragma unroll
+   for (int j = 0; j < MR; j++) {
+      int64_t at = it + ty + 4 * j;
+      if (i0 + tx < n0 && at < nt) {
+         C prod = v[0][j] * v[1][j];
+         C sum = prod + v[2][j];
+         store_as<C>(obase + at * p.stride[3][p.dt], p.dtype[3], sum, p.swap[3], p.unal[3]);
       }
    }
 }
@@ -318,6 +346,7 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
       bool bad = !aligned_to(p.ptr[k], (size_t)comp);
       for (int d = 0; d < L.ndims; d++) { p.stride[k][d] = L.stride[k][d]; if (L.stride[k][d] % comp) bad = true; }
       p.unal[k] = bad ? 1 : 0;
+      p.comp[k] = comp;
    }
    // operands that step by more than a few elements along dimension 0 but are dense
    // along some other dimension are staged through shared memory
@@ -333,11 +362,19 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
    }
    if (staged) {
       p.dt = dt; p.staged = staged;
-      p.tiles0 = ((uint64_t)L.size[0] + 31) / 32; p.tilest = ((uint64_t)L.size[dt] + 31) / 32;
+      p.tiles0 = ((uint64_t)L.size[0] + MT - 1) / MT; p.tilest = ((uint64_t)L.size[dt] + MT - 1) / MT;
       uint64_t blocks = p.tiles0 * p.tilest;
       for (int d = 1; d < L.ndims; d++) if (d != dt) blocks *= (uint64_t)L.size[d];
       if (blocks > 0x7FFFFFFFull) SD_ERROR("mixed_multiply_add: grid too large");
-      mix_tiled<C><<<(unsigned)blocks, 256, 0, stream>>>(p);
+      int nstaged = 0;
+      for (int k = 0; k < 3; k++) if (staged & (1u << k)) nstaged++;
+      size_t smem = (size_t)nstaged * MT * (MT + 1) * sizeof(C);            // up to 3 x 33 KB
+      static bool attr_set[2] = { false, false };
+      if (smem > 48 * 1024 && !attr_set[sizeof(C) == 8]) {
+         SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * MT * (MT + 1) * (int)sizeof(C)));
+         attr_set[sizeof(C) == 8] = true;
+      }
+      mix_tiled<C><<<(unsigned)blocks, 256, smem, stream>>>(p);
    } else {
       uint64_t blocks = (p.nelem + 255) / 256;
       uint64_t cap = (uint64_t)dev.sms * (dev.max_threads_per_sm / 256) * 4;

@@ -16,6 +16,8 @@ namespace sd {
 // When set (by solid_gpu_reduce_all_device on this thread) the value is left in
 // device memory at this address and nothing synchronises.
 extern thread_local void *reduce_all_device_result;
+// 64 pinned, device-mapped host bytes per device, created on first use (reduce_plan.cu).
+char *reduce_all_host_slot();
 
 template <class R> __global__ void red_identity(const R r, typename R::out_t *dst)
 {
@@ -30,7 +32,16 @@ int reduce_all(const R &r, const char *name, int ndims, const size_t *size, cons
    if (buffer == nullptr) SD_ERROR("Global reduction '%s' needs a device scratch buffer", name);
    RedParams p;
    if (red_make_params(p, 0, nullptr, nullptr, ptr, nullptr, buffer, ndims, size, strides) != 0) return -1;
-   char *slot = reduce_all_device_result ? (char *)reduce_all_device_result : (char *)buffer;
+   // Where the value goes: the caller's device address (device-resident form), or this device's
+   // pinned, device-mapped host slot, which the last kernel writes directly so that no separate
+   // device-to-host copy has to be queued before the synchronisation.
+   char *host_slot = nullptr;
+   char *slot = (char *)reduce_all_device_result;
+   if (slot == nullptr) {
+      host_slot = reduce_all_host_slot();
+      if (host_slot == nullptr) return -1;
+      slot = host_slot;
+   }
    p.dst = slot;
    p.buf = (char *)buffer + 16;
    if (p.relem == 0) {
@@ -42,9 +53,9 @@ int reduce_all(const R &r, const char *name, int ndims, const size_t *size, cons
       if (current_device_info(&dev) != 0) return -1;
       if (red_launch<R, T>(r, p, red_split_cap(1, p.relem, dev.sms), stream) != 0) return -1;
    }
-   if (reduce_all_device_result) return 0;
-   SD_CUDA_CHECK(cudaMemcpyAsync(result, slot, sizeof(O), cudaMemcpyDeviceToHost, stream));
+   if (host_slot == nullptr) return 0;
    SD_CUDA_CHECK(cudaStreamSynchronize(stream));
+   memcpy(result, host_slot, sizeof(O));
    return 0;
 }
 } // namespace sd
@@ -90,25 +101,6 @@ SD_DEFINE_BOUND2(all_gelt, 2, 1) SD_DEFINE_BOUND2(all_gele, 2, 2)
 // config->bufferSize, and has put the scratch pointer into config->data.ptrBuffer.
 // Everything is asynchronous on config->stream.
 // ---------------------------------------------------------------------------
-namespace sd {
-template <class R, class T>
-int reduce_axis(const R &r, solid_gpu_reduce_axis_config *config)
-{
-   const solid_gpu_reduce_axis_data &d = config->data;
-   RedParams p;
-   if (red_make_params(p, d.ndims, d.size, d.strides1, d.ptr1, d.strides2, d.ptr2,
-                       d.rdims, d.rsize, d.rstrides) != 0) return -1;
-   if (p.nout == 0) return 0;
-   if (p.relem == 0) SD_ERROR("Axis reduction over an empty range");
-   p.buf = d.ptrBuffer;
-   uint32_t cap = (uint32_t)config->sharedMem;                 // split bound chosen by prepare()
-   if (cap < 1 || p.buf == nullptr) cap = 1;
-   if (cap > 1 && (uint64_t)sizeof(typename R::acc_t) * p.nout * cap > config->bufferSize)
-      cap = (uint32_t)(config->bufferSize / (sizeof(typename R::acc_t) * p.nout));
-   if (cap < 1) cap = 1;
-   return red_launch<R, T>(r, p, cap, config->stream);
-}
-} // namespace sd
 
 #define SD_DEFINE_AXIS(NAME, GROUP) SD_WHEN(GROUP)(                                               \
    extern "C" int SD_PASTE(solid_gpu_axis_##NAME##_, SDX)(SOLID_GPU_ARGS_AXIS)                     \

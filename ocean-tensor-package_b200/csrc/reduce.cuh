@@ -202,7 +202,7 @@ __global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParam
    const uint64_t begin = (uint64_t)s * chunk;
    const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
    if (live) {
-      constexpr int U = 4;
+      constexpr int U = (sizeof(T) * VEC >= 16) ? 8 : 4;
       for (uint64_t r0 = begin + threadIdx.y; r0 < end; r0 += (uint64_t)blockDim.y * U) {
          Vec<T, VEC> v[U]; bool ok[U];
 #pragma unroll
@@ -352,7 +352,9 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
       bool vec = VEC > 1 && aligned_to(p.src, 16);
       for (int d = 0; d < p.ndims && vec; d++) if (p.stride1[d] % 16 != 0) vec = false;
       for (int d = 1; d < p.rdims && vec; d++) if (p.rstride[d] % 16 != 0) vec = false;
-      p.group = (p.relem >= 2048) ? 256 : 32;
+      // a warp per output when there are enough outputs to fill the machine with warps (no block
+      // barrier, 32 lanes x 4 vectors in flight each), a block per output otherwise
+      p.group = (p.relem < 2048 || p.nout >= (uint64_t)dev.sms * 32) ? 32 : 256;
       p.split = pick_split(p.nout * (p.group / 32) / 8 + 1);
       uint64_t groups = p.nout * p.split;
       uint64_t gpb = RED_THREADS / p.group;
@@ -391,6 +393,26 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
    }
    (void)sizeof(A);
    return 0;
+}
+
+// Launch one axis reduction from the caller's configuration (filled by
+// solid_gpu_reduce_axis_prepare, scratch pointer in data.ptrBuffer).
+template <class R, class T>
+int reduce_axis(const R &r, solid_gpu_reduce_axis_config *config)
+{
+   const solid_gpu_reduce_axis_data &d = config->data;
+   RedParams p;
+   if (red_make_params(p, d.ndims, d.size, d.strides1, d.ptr1, d.strides2, d.ptr2,
+                       d.rdims, d.rsize, d.rstrides) != 0) return -1;
+   if (p.nout == 0) return 0;
+   if (p.relem == 0) SD_ERROR("Axis reduction over an empty range");
+   p.buf = d.ptrBuffer;
+   uint32_t cap = (uint32_t)config->sharedMem;                 // split bound chosen by prepare()
+   if (cap < 1 || p.buf == nullptr) cap = 1;
+   if (cap > 1 && (uint64_t)sizeof(typename R::acc_t) * p.nout * cap > config->bufferSize)
+      cap = (uint32_t)(config->bufferSize / (sizeof(typename R::acc_t) * p.nout));
+   if (cap < 1) cap = 1;
+   return red_launch<R, T>(r, p, cap, config->stream);
 }
 
 } // namespace sd

@@ -6,7 +6,34 @@
 #include "solid_core_gpu.h"
 #include "reduce.cuh"
 
-namespace sd { thread_local void *reduce_all_device_result = nullptr; }
+namespace sd {
+thread_local void *reduce_all_device_result = nullptr;
+
+// Result slot of the host-returning global reductions: 64 bytes of pinned host memory per
+// device, mapped into the device address space (unified addressing makes the host pointer valid
+// in kernels).  Created the first time a device runs such a reduction and kept until exit.
+// Callers are single-threaded per device (docs/implementation.md of the reference), and each
+// call synchronises before it returns, so one slot per device suffices.
+char *reduce_all_host_slot()
+{
+   static char *slots[64] = {nullptr};
+   int device;
+   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
+      snprintf(solid_errmsg, SOLID_ERRMSG_SIZE, "Error getting the current device");
+      return nullptr;
+   }
+   if (slots[device] == nullptr) {
+      void *p = nullptr;
+      cudaError_t st = cudaHostAlloc(&p, 64, cudaHostAllocMapped | cudaHostAllocPortable);
+      if (st != cudaSuccess) {
+         snprintf(solid_errmsg, SOLID_ERRMSG_SIZE, "Error allocating the pinned result slot (%s)", cudaGetErrorString(st));
+         return nullptr;
+      }
+      slots[device] = (char *)p;
+   }
+   return slots[device];
+}
+} // namespace sd
 
 // 16 bytes for the result slot, then one accumulator (at most 16 bytes) per block
 // that can share the single output.

@@ -62,11 +62,18 @@ def float_to_half(f) -> np.ndarray:
 # work types (solid/include/solid/base/cpu/dtype_cpu.h:61-63) and conversion
 # (solid/include/solid/base/generic/dtype_assign.h:99-163,222-288)
 # ---------------------------------------------------------------------------
+def _complex(re, im, npdtype) -> np.ndarray:
+    """Complex array from parts without arithmetic (re + 1j*im would turn inf into nan)."""
+    out = np.empty(np.shape(re), dtype=npdtype)
+    out.real, out.imag = re, im
+    return out
+
+
 def to_work(dtype: str, x: np.ndarray) -> np.ndarray:
     if dtype == "half":
         return half_to_float(x)
     if dtype == "chalf":
-        return (half_to_float(x["real"]).astype(np.complex64) + 1j * half_to_float(x["imag"]).astype(np.complex64)).astype(np.complex64)
+        return _complex(half_to_float(x["real"]), half_to_float(x["imag"]), np.complex64)
     return np.asarray(x, dtype=NP[dtype])
 
 
@@ -135,7 +142,7 @@ def convert(src: str, dst: str, x: np.ndarray) -> np.ndarray:
         if dst == "chalf":
             out = np.zeros(x.shape, dtype=CHALF); out["real"], out["imag"] = r, i
             return out
-        return (r + 1j * i).astype(NP[dst])
+        return _complex(r, i, NP[dst])
     if src in COMPLEX:
         es, re = _real_part(src, x)
         if dst == "bool":
@@ -148,7 +155,7 @@ def convert(src: str, dst: str, x: np.ndarray) -> np.ndarray:
         if dst == "chalf":
             out = np.zeros(x.shape, dtype=CHALF); out["real"] = r
             return out
-        return r.astype(NP[dst])
+        return _complex(r, np.zeros_like(r), NP[dst])
     return _convert_real(src, dst, x)
 
 
@@ -329,10 +336,7 @@ def _binary_complex(name, dtype, x, y):                                  # binar
             zr, zi = np.where(take, yr, xr), np.where(take, yi, xi)
         else:
             raise KeyError(name)
-    w = (zr.astype(E) + 1j * zi.astype(E)).astype(np.complex128 if dtype == "cdouble" else np.complex64)
-    # rebuild exactly from parts (complex construction above must not round)
-    out = np.empty(w.shape, dtype=w.dtype); out.real, out.imag = zr.astype(E), zi.astype(E)
-    return from_work(dtype, out)
+    return from_work(dtype, _complex(zr.astype(E), zi.astype(E), np.complex128 if dtype == "cdouble" else np.complex64))
 
 
 def _compare(name, dtype, x, y):                                         # :128-133, 256-261, 310-315, 416-461

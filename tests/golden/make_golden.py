@@ -42,6 +42,8 @@ def main():
     for op in GOLDEN_UNARY:
         for dtype in dt.GROUPS[ol.UNARY_OPS[op]]:
             kind = "positive" if op in ("sqrt", "log") else ("special" if op in ("isinf", "isnan", "isfinite", "sign", "fabs") else "general")
+            if op == "exp" and dtype in dt.GROUPS["integer"]:
+                kind = "unit"                                   # keeps exp(x) inside every integer type
             x = util.random_values(dtype, N, np.random.default_rng(seed("u", op, dtype)), kind)
             od = "bool" if op.startswith("is") else (dt.elem_type(dtype) if op == "absolute" else dtype)
             y = np.zeros(N, dtype=dt.NUMPY[od])
@@ -72,9 +74,12 @@ def main():
             x = util.random_values(src, N, np.random.default_rng(seed("c", src, dst)), kind)
             y = np.zeros(N, dtype=dt.NUMPY[dst]); ys = np.zeros(N, dtype=dt.NUMPY[dst])
             cpu.copy(src, dst, [N], [dt.SIZE[src]], x.ctypes.data, [N], [dt.SIZE[dst]], y.ctypes.data)
-            cpu.copy(src, dst, [N], [dt.SIZE[src]], x.ctypes.data, [N], [dt.SIZE[dst]], ys.ctypes.data, variant="byteswap_copy")
+            xs = x.copy()                                       # the same values stored with reversed bytes
+            cpu.byteswap(src, [N], [dt.SIZE[src]], xs.ctypes.data)
+            cpu.copy(src, dst, [N], [dt.SIZE[src]], xs.ctypes.data, [N], [dt.SIZE[dst]], ys.ctypes.data, variant="byteswap_copy")
             out["copy/%s/%s/in" % (src, dst)] = x
             out["copy/%s/%s/out" % (src, dst)] = y
+            out["copy/%s/%s/in_swapped" % (src, dst)] = xs
             out["copy/%s/%s/out_swapped_source" % (src, dst)] = ys
     for op in GOLDEN_REDUCE:
         for dtype in dt.NAMES:

@@ -36,7 +36,7 @@ def random_values(dtype: str, n: int, rng: np.random.Generator, kind: str = "gen
         return (rng.random(n) < 0.5).astype(np.uint8)
     if dtype in dt.UINT:
         hi = {"general": 120, "positive": 120, "unit": 2, "small": 12, "special": 120}[kind]
-        return rng.integers(0, hi, n).astype(npdt)
+        return rng.integers(1 if kind == "positive" else 0, hi, n).astype(npdt)
     if dtype in dt.SINT:
         hi = {"general": 100, "positive": 100, "unit": 2, "small": 12, "special": 100}[kind]
         lo = 1 if kind == "positive" else -hi
