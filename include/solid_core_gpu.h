@@ -318,4 +318,27 @@ SOLID_API int solid_gpu_mixed_multiply_add(int ndims, const size_t *size,
 SOLID_API int solid_gpu_reduce_all_device(const char *op, int dtype, SOLID_GPU_ARGS_REDUCE_HEAD,
                                           void *result, void *buffer, cudaStream_t stream);
 
+/* ------------------------------------------------------------------------ */
+/* Axis sum of float tensors for callers that may not allocate.  It has no    */
+/* counterpart in the reference.  Some callers cannot obtain device memory at  */
+/* the point where they reduce: a callback or destructor that runs while an    */
+/* allocator lock is held, a latency-critical loop that must not take the      */
+/* device-wide synchronisation cudaMalloc/cudaFree imply, a process whose      */
+/* memory budget was handed out completely at start-up.  For them this variant */
+/* uses a scratch array that is part of the library image instead of           */
+/* config->data.ptrBuffer.                                                     */
+/*   - config comes from solid_gpu_reduce_axis_prepare as usual; source and    */
+/*     destination are the caller's; data.ptrBuffer is ignored and not modified */
+/*   - a plan whose bufferSize exceeds solid_gpu_noalloc_scratch_size() bytes   */
+/*     (1 MiB per device, held from library load to process exit) is refused    */
+/*     with -1 and a message                                                    */
+/*   - all calls on a device share the array: calls that overlap in time        */
+/*     (different streams or threads) race; issue them on one stream            */
+/*   - the first call on each device resolves the array's device address with   */
+/*     cudaGetSymbolAddress; make that first call before any stream capture     */
+/*   - no cudaMalloc, cudaFree or other allocating call is made                 */
+/* ------------------------------------------------------------------------ */
+SOLID_API int solid_gpu_noalloc_scratch_size(void);
+SOLID_API int solid_gpu_axis_sum_float_noalloc(solid_gpu_reduce_axis_config *config);
+
 #endif

@@ -190,6 +190,15 @@ class SolidGPU:
         st = f(C.byref(cfg)) if p is None else f(C.byref(cfg), C.c_double(p))
         self._check(st, "%s_%s" % (name, dtype))
 
+    def noalloc_scratch_size(self) -> int:
+        f = self.dll.solid_gpu_noalloc_scratch_size
+        f.restype = C.c_int
+        return f()
+
+    def axis_sum_float_noalloc(self, cfg: ReduceAxisConfig):
+        """Float axis sum that uses the scratch array built into the library (allocates nothing)."""
+        self._check(self.fn("solid_gpu_axis_sum_float_noalloc")(C.byref(cfg)), "axis_sum_float_noalloc")
+
     # -- fused -----------------------------------------------------------------------
     def axpy_sums_buffer_size(self, device: int) -> int:
         out = C.c_size_t(0)
