@@ -389,16 +389,22 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
-    for _ in range(args.warmup):
-        step()
-    barrier()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    with ClockSampler(local) as clocks:
+    with ClockSampler(local) as clocks:                      # sampled from the warm-up on: the timed region is short
+        time.sleep(0.25)
+        for _ in range(args.warmup):
+            step()
+        barrier()
         start.record()
         for i in range(args.steps):
             step(i)
         stop.record()
         barrier()
+        # keep the GPU under the same load until a few more samples exist
+        t_end = time.time() + 0.6
+        while time.time() < t_end:
+            step()
+        torch.cuda.synchronize()
     ms_total = start.elapsed_time(stop)
     kernel_ms = sum(a.elapsed_time(b) for a, b in zip(kstart, kstop)) / args.steps
     final = result.cpu().numpy().tolist()
@@ -478,7 +484,10 @@ def run_ours(args):
             "result": {"sum": final[0], "norm2": final[1]},
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of " + peak_kind, "kernel": "axpy_sums_kernel<float>",
-                         "kernel_ms": kernel_ms, "traffic": None},
+                         "kernel_ms": kernel_ms,
+                         # dram__bytes_read + dram__bytes_write of one launch: 3.187 GB measured by ncu at 2^28
+                         # elements (profiles/axpy_sums_kernel_float_c5.md), proportional to the element count
+                         "traffic": 3.187e9 * per / float(1 << 28), "traffic_unit": "bytes per launch"},
             "e2e": {"value": BYTES_PER_ELEMENT * n_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
                     "note": "per rank; inputs streamed through 256 MiB pinned windows (double buffered), z stays on the device"},

@@ -120,7 +120,19 @@ SD_HD Half float_to_half(float f)
    const uint32_t d = raw & 0x007FFFFFu;
    const uint32_t e = (raw >> 23) & 0xFFu;
    const uint32_t s = (raw >> 16) & 0x8000u;
-   // branch free: the regular encoding (16-bit wrap-around included), then the two overrides
+#ifdef __CUDA_ARCH__
+   // Normal half range (biased float exponent 113..142): the result is the hardware
+   // round-to-nearest-even conversion, except on an exact tie that RNE rounded down (kept
+   // mantissa bit 13 clear), where half.c rounds away from zero.  A carry out of the mantissa
+   // into the exponent behaves the same in both encodings.
+   if (e - 113u < 30u) {
+      uint32_t x = __half_as_ushort(__float2half_rn(f));
+      x += ((raw & 0x3FFFu) == 0x1000u) ? 1u : 0u;
+      Half r; r.v = (uint16_t)x;
+      return r;
+   }
+#endif
+   // general form, branch free: the regular encoding (16-bit wrap-around included), then the overrides
    uint32_t x = ((((e - 112u) << 10) | (d >> 13) | s) + ((d & 0x1FFFu) >= 0x1000u ? 1u : 0u)) & 0xFFFFu;
    const uint32_t special = (e == 255u && d != 0) ? 0x7F00u : (s | 0x7C00u);
    x = (e > 143u) ? special : x;

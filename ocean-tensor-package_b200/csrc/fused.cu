@@ -181,8 +181,55 @@ template <class C> SD_D C bits_as(uint64_t raw, int dtype, bool swap)
       default: return convert<C>(bits_typed<double>(raw, swap));
    }
 }
-template <class C> SD_D C load_as(const char *p, int dtype, int comp_size, bool swap, bool unal)
-{  return bits_as<C>(load_bits(p, comp_size, unal), dtype, swap); }
+// Array forms: ONE switch around the unrolled element loop.  (A switch per element inside a
+// fully unrolled loop multiplies the code of every case by the unroll factor; the kernels then
+// stall on instruction fetch instead of on memory.)
+template <int N> SD_D void load_bits_n(const char *const (&q)[N], const bool (&ok)[N], int comp_size, bool unal, uint64_t (&raw)[N])
+{
+   if (unal) {
+#pragma unroll
+      for (int j = 0; j < N; j++) raw[j] = ok[j] ? load_bits(q[j], comp_size, true) : 0;
+      return;
+   }
+   switch (comp_size) {
+      case 1:
+#pragma unroll
+         for (int j = 0; j < N; j++) raw[j] = ok[j] ? ld_one<uint8_t>(q[j]) : 0;
+         break;
+      case 2:
+#pragma unroll
+         for (int j = 0; j < N; j++) raw[j] = ok[j] ? ld_one<uint16_t>(q[j]) : 0;
+         break;
+      case 4:
+#pragma unroll
+         for (int j = 0; j < N; j++) raw[j] = ok[j] ? ld_one<uint32_t>(q[j]) : 0;
+         break;
+      default:
+#pragma unroll
+         for (int j = 0; j < N; j++) raw[j] = ok[j] ? ld_one<uint64_t>(q[j]) : 0;
+         break;
+   }
+}
+#define SD_BITS_CASE(TYPE)                                                             \
+   _Pragma("unroll") for (int j = 0; j < N; j++) out[j] = convert<C>(bits_typed<TYPE>(raw[j], swap)); break;
+template <class C, int N> SD_D void bits_as_n(const uint64_t (&raw)[N], int dtype, bool swap, C (&out)[N])
+{
+   switch (dtype) {
+      case 0:  SD_BITS_CASE(Bool)
+      case 1:  SD_BITS_CASE(uint8_t)
+      case 2:  SD_BITS_CASE(uint16_t)
+      case 3:  SD_BITS_CASE(uint32_t)
+      case 4:  SD_BITS_CASE(uint64_t)
+      case 5:  SD_BITS_CASE(int8_t)
+      case 6:  SD_BITS_CASE(int16_t)
+      case 7:  SD_BITS_CASE(int32_t)
+      case 8:  SD_BITS_CASE(int64_t)
+      case 9:  case 12: SD_BITS_CASE(Half)
+      case 10: case 13: SD_BITS_CASE(float)
+      default: SD_BITS_CASE(double)
+   }
+}
+#undef SD_BITS_CASE
 template <class D, class C> SD_D void store_typed(char *p, C v, bool swap, bool unal)
 {
    D y = convert<D>(v);
@@ -192,6 +239,29 @@ template <class D, class C> SD_D void store_typed(char *p, C v, bool swap, bool 
 #pragma unroll
       for (int i = 0; i < (int)sizeof(D); i++) reinterpret_cast<uint8_t *>(p)[i] = b[i]; }
 }
+#define SD_STORE_CASE(TYPE)                                                            \
+   _Pragma("unroll") for (int j = 0; j < N; j++) if (ok[j]) store_typed<TYPE>(q[j], v[j], swap, unal); break;
+template <class C, int N> SD_D void store_as_n(char *const (&q)[N], const bool (&ok)[N], int dtype, const C (&v)[N], bool swap, bool unal)
+{
+   switch (dtype) {
+      case 0:  SD_STORE_CASE(Bool)
+      case 1:  SD_STORE_CASE(uint8_t)
+      case 2:  SD_STORE_CASE(uint16_t)
+      case 3:  SD_STORE_CASE(uint32_t)
+      case 4:  SD_STORE_CASE(uint64_t)
+      case 5:  SD_STORE_CASE(int8_t)
+      case 6:  SD_STORE_CASE(int16_t)
+      case 7:  SD_STORE_CASE(int32_t)
+      case 8:  SD_STORE_CASE(int64_t)
+      case 9:  SD_STORE_CASE(Half)
+      case 10: SD_STORE_CASE(float)
+      case 11: SD_STORE_CASE(double)
+      case 12: SD_STORE_CASE(CHalf)
+      case 13: SD_STORE_CASE(CFloat)
+      default: SD_STORE_CASE(CDouble)
+   }
+}
+#undef SD_STORE_CASE
 template <class C> SD_D void store_as(char *p, int dtype, C v, bool swap, bool unal)
 {
    switch (dtype) {
@@ -213,48 +283,111 @@ template <class C> SD_D void store_as(char *p, int dtype, C v, bool swap, bool u
    }
 }
 
-// Linear variant: no operand needs staging.  One element per thread-iteration,
-// adjacent threads adjacent along dimension 0.
+// Linear variant for one merged dimension: a block handles 256 x MR consecutive elements, a
+// thread MR of them 256 apart (coalesced), all loads issued before the first conversion.
+constexpr int M0 = 32;                      // tile extent along dimension 0
+constexpr int M1 = 64;                      // tile extent along dimension dt
+constexpr int MR = 8;                       // elements per thread (M0 * M1 / 256)
+
 template <class C>
 __global__ void __launch_bounds__(256) mix_linear(const MixParams p)
 {
-   for (uint64_t idx = (uint64_t)blockIdx.x * 256 + threadIdx.x; idx < p.nelem; idx += (uint64_t)gridDim.x * 256) {
-      int64_t off[4] = {0, 0, 0, 0};
-      uint64_t r = idx;
-      for (int d = 0; d < p.ndims - 1; d++) {
-         uint64_t q = r / (uint64_t)p.size[d]; uint64_t c = r - q * (uint64_t)p.size[d]; r = q;
+   const uint64_t chunk = 256ull * MR;
+   for (uint64_t base = (uint64_t)blockIdx.x * chunk; base < p.nelem; base += (uint64_t)gridDim.x * chunk) {
+      bool ok[MR];
 #pragma unroll
-         for (int k = 0; k < 4; k++) off[k] += (int64_t)c * p.stride[k][d];
+      for (int j = 0; j < MR; j++) ok[j] = base + threadIdx.x + 256ull * j < p.nelem;
+      C acc[MR];
+#pragma unroll
+      for (int k = 0; k < 3; k++) {
+         const char *q[MR];
+#pragma unroll
+         for (int j = 0; j < MR; j++) q[j] = p.ptr[k] + (int64_t)(base + threadIdx.x + 256ull * j) * p.stride[k][0];
+         uint64_t raw[MR]; C v[MR];
+         load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
+         bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
+#pragma unroll
+         for (int j = 0; j < MR; j++) acc[j] = (k == 0) ? v[j] : (k == 1 ? acc[j] * v[j] : acc[j] + v[j]);
       }
+      char *qo[MR];
 #pragma unroll
-      for (int k = 0; k < 4; k++) off[k] += (int64_t)r * p.stride[k][p.ndims - 1];
-      uint64_t ra = load_bits(p.ptr[0] + off[0], p.comp[0], p.unal[0]);
-      uint64_t rb = load_bits(p.ptr[1] + off[1], p.comp[1], p.unal[1]);
-      uint64_t rc = load_bits(p.ptr[2] + off[2], p.comp[2], p.unal[2]);
-      C a = bits_as<C>(ra, p.dtype[0], p.swap[0]);
-      C b = bits_as<C>(rb, p.dtype[1], p.swap[1]);
-      C c = bits_as<C>(rc, p.dtype[2], p.swap[2]);
-      C prod = a * b;
-      C sum = prod + c;
-      store_as<C>(p.ptr[3] + off[3], p.dtype[3], sum, p.swap[3], p.unal[3]);
+      for (int j = 0; j < MR; j++) qo[j] = p.ptr[3] + (int64_t)(base + threadIdx.x + 256ull * j) * p.stride[3][0];
+      store_as_n<C, MR>(qo, ok, p.dtype[3], acc, p.swap[3], p.unal[3]);
    }
 }
 
-// Tiled variant: a 64 x 64 tile over (dimension 0, dimension dt), 256 threads, 16 elements
-// per thread and operand.  Operands that are dense along dt are first read with lanes
-// running along dt (coalesced), converted and parked in shared memory; then lanes run
-// along dimension 0, the remaining operands are read directly (coalesced) and the result
-// is stored.  In both phases a thread issues all of its loads before it consumes any of
-// them, so sixteen independent requests per operand are in flight per thread.
-constexpr int MT = 64;                      // tile edge
-constexpr int MR = 16;                      // elements per thread (MT * MT / 256)
+// Tiled variant for two or more dimensions: a tile of 32 (dimension 0) x 64 (dimension dt)
+// elements, 256 threads, 8 elements per thread and operand.  Operands that are dense along dt
+// (a transposed matrix) are first read with 64 lanes running along dt, converted and parked in
+// shared memory; then 32 lanes run along dimension 0, the remaining operands are read
+// directly (coalesced) and the result is stored.  In both phases a thread issues all loads of
+// an operand before it consumes any of them.
+template <class C, bool FULL>
+SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t (&off)[4],
+                        int64_t i0, int64_t it, int64_t n0, int64_t nt)
+{
+   // phase 1: 64 lanes along dt, 4 rows of dimension 0 per pass
+   if (p.staged) {
+      const int tx = threadIdx.x & (M1 - 1), ty = threadIdx.x / M1;
+      bool ok[MR];
+#pragma unroll
+      for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + ty + 4 * j < n0) && (it + tx < nt));
+      int slot = 0;
+      for (int k = 0; k < 3; k++) {
+         if (!(p.staged & (1u << k))) continue;
+         const char *q[MR];
+         q[0] = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt] + (i0 + ty) * p.stride[k][0];
+         const int64_t step = 4 * p.stride[k][0];
+#pragma unroll
+         for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
+         uint64_t raw[MR]; C v[MR];
+         load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
+         bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
+#pragma unroll
+         for (int j = 0; j < MR; j++) tile[slot][ty + 4 * j][tx] = v[j];
+         slot++;
+      }
+      __syncthreads();
+   }
+   // phase 2: 32 lanes along dimension 0, 8 columns of dt per pass
+   const int tx = threadIdx.x & (M0 - 1), ty = threadIdx.x / M0;
+   bool ok[MR];
+#pragma unroll
+   for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + tx < n0) && (it + ty + 8 * j < nt));
+   C acc[MR];
+   int slot = 0;
+   for (int k = 0; k < 3; k++) {
+      C v[MR];
+      if (p.staged & (1u << k)) {
+#pragma unroll
+         for (int j = 0; j < MR; j++) v[j] = tile[slot][tx][ty + 8 * j];
+         slot++;
+      } else {
+         const char *q[MR];
+         q[0] = p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0] + (it + ty) * p.stride[k][p.dt];
+         const int64_t step = 8 * p.stride[k][p.dt];
+#pragma unroll
+         for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
+         uint64_t raw[MR];
+         load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
+         bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
+      }
+#pragma unroll
+      for (int j = 0; j < MR; j++) acc[j] = (k == 0) ? v[j] : (k == 1 ? acc[j] * v[j] : acc[j] + v[j]);   // rounded product, rounded sum
+   }
+   char *qo[MR];
+   qo[0] = p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0] + (it + ty) * p.stride[3][p.dt];
+   const int64_t ostep = 8 * p.stride[3][p.dt];
+#pragma unroll
+   for (int j = 1; j < MR; j++) qo[j] = qo[j - 1] + ostep;
+   store_as_n<C, MR>(qo, ok, p.dtype[3], acc, p.swap[3], p.unal[3]);
+}
 
 template <class C>
-__global__ void __launch_bounds__(256) mix_tiled(const MixParams p)
+__global__ void __launch_bounds__(256, 4) mix_tiled(const MixParams p)
 {
    extern __shared__ __align__(16) unsigned char mix_smem[];
-   C (*tile)[MT][MT + 1] = reinterpret_cast<C (*)[MT][MT + 1]>(mix_smem);
-   const int tx = threadIdx.x & (MT - 1), ty = threadIdx.x / MT;      // 64 x 4
+   C (*tile)[M0][M1 + 1] = reinterpret_cast<C (*)[M0][M1 + 1]>(mix_smem);
    uint64_t bid = blockIdx.x;
    const uint64_t t0 = bid % p.tiles0; bid /= p.tiles0;
    const uint64_t tt = bid % p.tilest; bid /= p.tilest;
@@ -265,61 +398,11 @@ __global__ void __launch_bounds__(256) mix_tiled(const MixParams p)
 #pragma unroll
       for (int k = 0; k < 4; k++) off[k] += (int64_t)c * p.stride[k][d];
    }
-   const int64_t i0 = (int64_t)t0 * MT, it = (int64_t)tt * MT;
+   const int64_t i0 = (int64_t)t0 * M0, it = (int64_t)tt * M1;
    const int64_t n0 = p.size[0], nt = p.size[p.dt];
-
-   // phase 1: lanes along dt; tile slot of operand k is the number of staged operands below k
-   int slot = 0;
-#pragma unroll
-   for (int k = 0; k < 3; k++) {
-      if (!(p.staged & (1u << k))) continue;
-      uint64_t raw[MR];
-      const char *base = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt];
-#pragma unroll
-      for (int j = 0; j < MR; j++) {
-         int64_t a0 = i0 + ty + 4 * j;
-         raw[j] = (a0 < n0 && it + tx < nt) ? load_bits(base + a0 * p.stride[k][0], p.comp[k], p.unal[k]) : 0;
-      }
-#pragma unroll
-      for (int j = 0; j < MR; j++) tile[slot][ty + 4 * j][tx] = bits_as<C>(raw[j], p.dtype[k], p.swap[k]);
-      slot++;
-   }
-   __syncthreads();
-   // phase 2: lanes along dimension 0
-   uint64_t raw[3][MR];
-#pragma unroll
-   for (int k = 0; k < 3; k++) {
-      if (p.staged & (1u << k)) continue;
-      const char *base = p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0];
-#pragma unroll
-      for (int j = 0; j < MR; j++) {
-         int64_t at = it + ty + 4 * j;
-         raw[k][j] = (i0 + tx < n0 && at < nt) ? load_bits(base + at * p.stride[k][p.dt], p.comp[k], p.unal[k]) : 0;
-      }
-   }
-   C v[3][MR];
-   slot = 0;
-#pragma unroll
-   for (int k = 0; k < 3; k++) {
-      if (p.staged & (1u << k)) {
-#pragma unroll
-         for (int j = 0; j < MR; j++) v[k][j] = tile[slot][tx][ty + 4 * j];
-         slot++;
-      } else {
-#pragma unroll
-         for (int j = 0; j < MR; j++) v[k][j] = bits_as<C>(raw[k][j], p.dtype[k], p.swap[k]);
-      }
-   }
-   char *obase = p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0];
-#pragma unroll
-   for (int j = 0; j < MR; j++) {
-      int64_t at = it + ty + 4 * j;
-      if (i0 + tx < n0 && at < nt) {
-         C prod = v[0][j] * v[1][j];
-         C sum = prod + v[2][j];
-         store_as<C>(obase + at * p.stride[3][p.dt], p.dtype[3], sum, p.swap[3], p.unal[3]);
-      }
-   }
+   // interior tiles take the copy of the body without bounds predicates
+   if (i0 + M0 <= n0 && it + M1 <= nt) mix_tile_body<C, true>(p, tile, off, i0, it, n0, nt);
+   else                                mix_tile_body<C, false>(p, tile, off, i0, it, n0, nt);
 }
 
 template <class C>
@@ -360,23 +443,24 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
          if (sd_ == es && L.size[d] >= 16 && (dt < 0 || dt == d)) { dt = d; staged |= (1u << k); break; }
       }
    }
-   if (staged) {
+   if (L.ndims >= 2) {
+      if (!staged) dt = 1;                                           // plain 2-D tiling, nothing staged
       p.dt = dt; p.staged = staged;
-      p.tiles0 = ((uint64_t)L.size[0] + MT - 1) / MT; p.tilest = ((uint64_t)L.size[dt] + MT - 1) / MT;
+      p.tiles0 = ((uint64_t)L.size[0] + M0 - 1) / M0; p.tilest = ((uint64_t)L.size[dt] + M1 - 1) / M1;
       uint64_t blocks = p.tiles0 * p.tilest;
       for (int d = 1; d < L.ndims; d++) if (d != dt) blocks *= (uint64_t)L.size[d];
       if (blocks > 0x7FFFFFFFull) SD_ERROR("mixed_multiply_add: grid too large");
       int nstaged = 0;
       for (int k = 0; k < 3; k++) if (staged & (1u << k)) nstaged++;
-      size_t smem = (size_t)nstaged * MT * (MT + 1) * sizeof(C);            // up to 3 x 33 KB
+      size_t smem = (size_t)nstaged * M0 * (M1 + 1) * sizeof(C);            // up to 3 x 16.3 KB
       static bool attr_set[2] = { false, false };
       if (smem > 48 * 1024 && !attr_set[sizeof(C) == 8]) {
-         SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * MT * (MT + 1) * (int)sizeof(C)));
+         SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * M0 * (M1 + 1) * (int)sizeof(C)));
          attr_set[sizeof(C) == 8] = true;
       }
       mix_tiled<C><<<(unsigned)blocks, 256, smem, stream>>>(p);
    } else {
-      uint64_t blocks = (p.nelem + 255) / 256;
+      uint64_t blocks = (p.nelem + 256ull * MR - 1) / (256ull * MR);
       uint64_t cap = (uint64_t)dev.sms * (dev.max_threads_per_sm / 256) * 4;
       if (blocks > cap) blocks = cap;
       mix_linear<C><<<(unsigned)blocks, 256, 0, stream>>>(p);

@@ -21,6 +21,7 @@
 //     out_t  finalize(acc_t)
 #pragma once
 #include "mathfn.cuh"
+#include "word_accum.cuh"
 
 namespace sd {
 
@@ -278,5 +279,33 @@ template <class T, bool SKIP_NAN> struct r_norm_ {
 };
 template <class T> using r_norm     = r_norm_<T, false>;
 template <class T> using r_norm_nan = r_norm_<T, (is_real<T> || is_cplx<T>)>;
+
+// ---------------------------------------------------------------------------
+// Four 1-byte elements at a time.  For the reductions below a 32-bit word of packed
+// bool / uint8 / int8 elements can be folded with one or two SIMD-in-register
+// instructions instead of four extract-test-accumulate sequences; the kernels use
+// this when word_accum<R, T>::ok.
+// ---------------------------------------------------------------------------
+
+template <class T> struct word_accum<r_count<T, false>, T> {               // nnz: bytes that are not zero
+   static constexpr bool ok = sizeof(T) == 1;
+   SD_D static void apply(const r_count<T, false> &, uint64_t &a, uint32_t w) { a += __popc(__vcmpne4(w, 0u)) >> 3; }
+};
+template <class T> struct word_accum<r_logical<T, true, p_nonzero<T>>, T> {  // any
+   static constexpr bool ok = sizeof(T) == 1;
+   SD_D static void apply(const r_logical<T, true, p_nonzero<T>> &, uint8_t &a, uint32_t w) { if (w) a = 1; }
+};
+template <class T> struct word_accum<r_logical<T, false, p_nonzero<T>>, T> { // all
+   static constexpr bool ok = sizeof(T) == 1;
+   SD_D static void apply(const r_logical<T, false, p_nonzero<T>> &, uint8_t &a, uint32_t w) { if (__vcmpeq4(w, 0u)) a = 0; }
+};
+template <class T> struct word_accum<r_sum_<T, false>, T> {                  // sum of bytes
+   static constexpr bool ok = sizeof(T) == 1;
+   SD_D static void apply(const r_sum_<T, false> &, typename r_sum_<T, false>::acc_t &a, uint32_t w)
+   {
+      if constexpr (is_sint<T>) a += (int64_t)__dp4a((int)w, 0x01010101, 0);
+      else                      a += (uint64_t)__dp4a(w, 0x01010101u, 0u);
+   }
+};
 
 } // namespace sd

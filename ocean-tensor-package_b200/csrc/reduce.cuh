@@ -25,6 +25,7 @@
 #pragma once
 #include "dtypes.cuh"
 #include "layout.h"
+#include "word_accum.cuh"
 
 namespace sd {
 
@@ -108,6 +109,21 @@ template <class R> SD_D void red_emit(const R &r, const RedParams &p, uint64_t o
    else *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
 }
 
+// Fold all VEC elements of one vector into the accumulator (packed-word form for 1-byte types
+// where the reduction has one).
+template <class R, class T, int VEC> SD_D void accum_vec(const R &r, typename R::acc_t &acc, const Vec<T, VEC> &v)
+{
+   if constexpr (word_accum<R, T>::ok && VEC % 4 == 0) {
+      uint32_t w[VEC / 4];
+      memcpy(w, &v, VEC);
+#pragma unroll
+      for (int i = 0; i < VEC / 4; i++) word_accum<R, T>::apply(r, acc, w[i]);
+   } else {
+#pragma unroll
+      for (int e = 0; e < VEC; e++) r.accum(acc, v.v[e]);
+   }
+}
+
 // ---------------------------------------------------------------------------
 template <class R, class T, int VEC>
 __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParams p)
@@ -136,7 +152,24 @@ __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParam
       const uint64_t begin = (uint64_t)s * chunk;
       const uint64_t end = begin + chunk < total ? begin + chunk : total;
       constexpr int U = 4;
-      for (uint64_t slot0 = begin + lane; slot0 < end; slot0 += (uint64_t)group * U) {
+      uint64_t slot0 = begin + lane;
+      if (rows == 1) {
+         // One dense row: whole vectors by pointer increment, nothing predicated per element.
+         const uint64_t nfull = rowlen / VEC;
+         const uint64_t fend = end < nfull ? end : nfull;
+         const char *q = base + slot0 * (VEC * sizeof(T));
+         const uint64_t gstep = (uint64_t)group * (VEC * sizeof(T));
+         for (; slot0 + (uint64_t)(U - 1) * group < fend; slot0 += (uint64_t)group * U, q += gstep * U) {
+            Vec<T, VEC> v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) v[u] = ld_vec<T, VEC>(q + u * gstep);
+#pragma unroll
+            for (int u = 0; u < U; u++) accum_vec<R, T, VEC>(r, acc, v[u]);
+         }
+         for (; slot0 < fend; slot0 += group, q += gstep) accum_vec<R, T, VEC>(r, acc, ld_vec<T, VEC>(q));
+         // the ragged last slot (fewer than VEC elements) is left to the general loop below
+      }
+      for (; slot0 < end; slot0 += (uint64_t)group * U) {
          Vec<T, VEC> v[U]; int cnt[U];
 #pragma unroll
          for (int u = 0; u < U; u++) {
@@ -203,7 +236,24 @@ __global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParam
    const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
    if (live) {
       constexpr int U = (sizeof(T) * VEC >= 16) ? 8 : 4;
-      for (uint64_t r0 = begin + threadIdx.y; r0 < end; r0 += (uint64_t)blockDim.y * U) {
+      uint64_t r0 = begin + threadIdx.y;
+      if (nmine == VEC && p.rdims == 1) {
+         // full vector of outputs, one reduced dimension: pointer increments only
+         const int64_t rs = p.rstride[0];
+         const char *q = base + (int64_t)r0 * rs;
+         const int64_t ystep = (int64_t)blockDim.y * rs;
+         for (; r0 + (uint64_t)(U - 1) * blockDim.y < end; r0 += (uint64_t)blockDim.y * U, q += ystep * U) {
+            Vec<T, VEC> v[U];
+#pragma unroll
+            for (int u = 0; u < U; u++) v[u] = ld_vec<T, VEC>(q + u * ystep);
+#pragma unroll
+            for (int u = 0; u < U; u++) {
+#pragma unroll
+               for (int e = 0; e < VEC; e++) r.accum(acc[e], v[u].v[e]);
+            }
+         }
+      }
+      for (; r0 < end; r0 += (uint64_t)blockDim.y * U) {
          Vec<T, VEC> v[U]; bool ok[U];
 #pragma unroll
          for (int u = 0; u < U; u++) {

@@ -188,7 +188,11 @@ def unary(name: str, src: Tensor, dst: Tensor | None = None) -> Tensor:
 
 def binary(name: str, a: Tensor, b: Tensor, dst: Tensor | None = None) -> Tensor:
     size = _broadcast_size(a, b)
-    ctype = common_type(a.dtype, b.dtype)
+    # shifts keep the type of the shifted tensor (the count is cast to int8); every other
+    # operation works in the common type of both operands
+    ctype = a.dtype if name in ("bitshift_left", "bitshift_right") else common_type(a.dtype, b.dtype)
+    if name == "power" and a.dtype in dt.GROUPS["integer_bool"] and b.dtype in dt.GROUPS["integer_bool"]:
+        ctype = a.dtype                                  # integer base with an integer exponent (cast to int16)
     if ctype not in dt.GROUPS[ol.BINARY_OPS[name]]:
         raise TypeError("%s is not available for type %s" % (name, ctype))
     x = _prepared(a, ctype, size)
