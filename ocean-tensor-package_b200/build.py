@@ -25,6 +25,7 @@ INCLUDE = HERE.parent / "include"
 BUILD = HERE / "build"
 LIBDIR = HERE / "lib"
 LIB = LIBDIR / "libsolid_core_gpu.so"
+OCEAN_LIB = LIBDIR / "libocean_gpu_b200.so"        # Ocean-level dispatch on top of the Solid tables
 
 # name -> kind (0 bool, 1 unsigned, 2 signed, 3 real floating point, 4 complex)
 TYPES = {"bool": 0, "uint8": 1, "uint16": 1, "uint32": 1, "uint64": 1,
@@ -104,6 +105,16 @@ def build(jobs_n: int | None = None, force: bool = False, types=None, verbose: b
             raise RuntimeError("link failed:\n" + res.stdout)
         if verbose:
             print("[build] linked", LIB, flush=True)
+    # the dispatch layer is host code only; it links against the Solid library beside it
+    obj, secs, did = _compile((CSRC / "ocean_gpu.cu", BUILD / "ocean_gpu.o", []), stamp, force)
+    if did or rebuilt or not OCEAN_LIB.exists():
+        cmd = [nvcc(), "-shared", "-o", str(OCEAN_LIB), str(obj), "-L%s" % LIBDIR, "-lsolid_core_gpu",
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart"]
+        res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if res.returncode != 0:
+            raise RuntimeError("link failed:\n" + res.stdout)
+        if verbose:
+            print("[build] linked", OCEAN_LIB, flush=True)
     return LIB
 
 

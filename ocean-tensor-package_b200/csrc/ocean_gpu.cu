@@ -1,0 +1,439 @@
+// Ocean-level GPU dispatch (declared in include/ocean_gpu_b200.h): table lookup by dtype,
+// device activation, stream ordering, scratch from a per-device cache, host results -- what
+// src/core/gpu/op/tensor_{unary,binary,copy,fill,reduce_all,reduce_axis}_gpu.c do in the
+// reference.  Layout simplification (OcSolid_analyze*, src/external/ocean-solid/ocean_solid.c)
+// is done inside the Solid entry points here, so the views are passed through as they are.
+#include <cstdio>
+#include <cstdarg>
+#include <cstring>
+#include <mutex>
+#include "ocean_gpu_b200.h"
+
+namespace {
+
+thread_local char g_error[SOLID_ERRMSG_SIZE] = "";
+
+int fail(const char *fmt, ...)
+{
+   va_list ap; va_start(ap, fmt);
+   vsnprintf(g_error, sizeof(g_error), fmt, ap);
+   va_end(ap);
+   return -1;
+}
+int fail_solid() { snprintf(g_error, sizeof(g_error), "%s", solid_errmsg); return -1; }     // OC_SOLID_ERRMSG
+int fail_cuda(cudaError_t st, const char *what) { return fail("%s: %s", what, cudaGetErrorString(st)); }
+
+const char *const dtype_names[SOLID_NUM_TYPES] = {
+   "bool", "uint8", "uint16", "uint32", "uint64", "int8", "int16", "int32", "int64",
+   "half", "float", "double", "complex-half", "complex-float", "complex-double" };
+
+bool valid_dtype(int t) { return t >= 0 && t < SOLID_NUM_TYPES; }
+
+// OC_SOLID_FUNPTR (src/external/ocean-solid/ocean_solid.h:131-140): NULL entry -> typed error
+template <class F> F lookup(F const *table, int dtype, const char *desc)
+{
+   if (!valid_dtype(dtype)) { fail("Invalid data type index %d", dtype); return nullptr; }
+   F f = table[dtype];
+   if (f == nullptr) fail("Function %s is not supported for type %s on GPU", desc, dtype_names[dtype]);
+   return f;
+}
+
+int set_device(int device)                                             // OcCuda_setDevice
+{
+   cudaError_t st = cudaSetDevice(device);
+   return st == cudaSuccess ? 0 : fail_cuda(st, "Error activating the GPU device");
+}
+
+// Stream protocol of src/base/storage.c:141-222 on the facts a view carries.
+int start_read(const OcTensorView *dst, const OcTensorView *src)
+{
+   if (src->stream == dst->stream || src->event == nullptr) return 0;
+   cudaError_t st = cudaStreamWaitEvent(dst->stream, src->event, 0);
+   return st == cudaSuccess ? 0 : fail_cuda(st, "Error synchronizing streams");
+}
+int update(const OcTensorView *dst)
+{
+   if (dst->event == nullptr) return 0;
+   cudaError_t st = cudaEventRecord(dst->event, dst->stream);
+   return st == cudaSuccess ? 0 : fail_cuda(st, "Error recording the tensor event");
+}
+int finish_read(const OcTensorView *dst, const OcTensorView *src)
+{
+   // the source must not be overwritten on its own stream before this read has completed
+   if (src->stream == dst->stream || dst->event == nullptr) return 0;
+   cudaError_t st = cudaStreamWaitEvent(src->stream, dst->event, 0);
+   return st == cudaSuccess ? 0 : fail_cuda(st, "Error synchronizing streams");
+}
+
+bool same_shape(const OcTensorView *a, const OcTensorView *b)
+{
+   if (a->ndims != b->ndims) return false;
+   for (int i = 0; i < a->ndims; i++) if (a->size[i] != b->size[i]) return false;
+   return true;
+}
+int check_view(const OcTensorView *t, const char *what)
+{
+   if (t == nullptr) return fail("Missing %s tensor", what);
+   if (t->ndims < 0 || t->ndims > SOLID_MAX_TENSOR_DIMS) return fail("Invalid number of dimensions (%d)", t->ndims);
+   if (!valid_dtype(t->dtype)) return fail("Invalid data type index %d", t->dtype);
+   return 0;
+}
+// Preconditions the interface layer guarantees for elementwise kernels (tensor_op.c:346-409)
+int check_elemwise(const OcTensorView *t, const char *what)
+{
+   if (check_view(t, what) != 0) return -1;
+   if (t->byteswapped) return fail("The %s tensor must be in native byte order", what);
+   return 0;
+}
+
+// ---- scratch: three round-robin slots per device (src/core/interface/storage_itf.c:61-121) ----
+struct Slot { void *ptr; size_t size; };
+struct DeviceCache { Slot slot[3]; int next; };
+DeviceCache g_cache[64];
+std::mutex g_cache_lock;
+
+int temporary(int device, size_t bytes, void **out)
+{
+   if (device < 0 || device >= 64) return fail("Invalid device index %d", device);
+   std::lock_guard<std::mutex> guard(g_cache_lock);
+   DeviceCache &c = g_cache[device];
+   Slot &s = c.slot[c.next];
+   c.next = (c.next + 1) % 3;
+   if (s.size < bytes) {
+      // the slot was last handed out three requests ago; wait for the device before replacing it
+      if (s.ptr) { cudaDeviceSynchronize(); cudaFree(s.ptr); s.ptr = nullptr; s.size = 0; }
+      size_t want = bytes < (1u << 16) ? (1u << 16) : bytes;
+      cudaError_t st = cudaMalloc(&s.ptr, want);
+      if (st != cudaSuccess) { s.ptr = nullptr; return fail_cuda(st, "Error allocating a temporary buffer"); }
+      s.size = want;
+   }
+   *out = s.ptr;
+   return 0;
+}
+
+// result dtypes of reductions (solid/include/solid/core/generic/reduce_ops.h:607-617,798-837,1004-1255)
+bool is_intlike(int t) { return t <= SD_INT64; }
+bool is_complex(int t) { return t >= SD_CHALF; }
+int elem_type(int t) { return is_complex(t) ? t - 3 : t; }
+int abs_type(int t) { return (t >= SD_INT8 && t <= SD_INT64) ? t - 4 : elem_type(t); }
+int sum_type(int t) { return t <= SD_UINT64 ? SD_UINT64 : (t <= SD_INT64 ? SD_INT64 : t); }
+
+} // namespace
+
+extern "C" int OcGPU_reductionResultType(const char *name, int t)
+{
+   if (!valid_dtype(t) || name == nullptr) return -1;
+   if (strncmp(name, "axis_", 5) == 0) name += 5;
+   if (!strncmp(name, "any", 3) || !strncmp(name, "all", 3)) return SD_BOOL;
+   if (!strncmp(name, "nnz", 3)) return SD_UINT64;
+   if (!strcmp(name, "sum") || !strcmp(name, "sum_nan") || !strcmp(name, "prod") || !strcmp(name, "prod_nan")) return sum_type(t);
+   if (!strcmp(name, "sum_abs") || !strcmp(name, "sum_abs_nan")) return is_intlike(t) ? SD_UINT64 : abs_type(t);
+   if (!strcmp(name, "maximum") || !strcmp(name, "minimum")) return t;
+   if (!strcmp(name, "maximum_abs") || !strcmp(name, "minimum_abs")) return abs_type(t);
+   if (!strncmp(name, "norm", 4)) return is_intlike(t) ? SD_DOUBLE : abs_type(t);
+   return -1;
+}
+
+extern "C" const char *OcGPU_errorMessage(void) { return g_error; }
+
+extern "C" int OcInitGPU_B200(void)
+{
+   if (solid_gpu_initialize() != 0) return fail_solid();
+   int n = 0;
+   if (cudaGetDeviceCount(&n) != cudaSuccess) { cudaGetLastError(); n = 0; }
+   int current = 0; cudaGetDevice(&current);
+   for (int d = 0; d < n; d++) {                        // warm-up as OcInitDevicesGPU does (device_gpu.c:155-196)
+      if (set_device(d) != 0) return -1;
+      if (solid_gpu_dummy_kernel() != 0) return fail_solid();
+   }
+   if (n) cudaSetDevice(current);
+   return 0;
+}
+
+extern "C" void OcFinalizeGPU_B200(void)
+{
+   std::lock_guard<std::mutex> guard(g_cache_lock);
+   int current = 0; cudaGetDevice(&current);
+   for (int d = 0; d < 64; d++) for (Slot &s : g_cache[d].slot) if (s.ptr) {
+      cudaSetDevice(d); cudaDeviceSynchronize(); cudaFree(s.ptr); s.ptr = nullptr; s.size = 0; }
+   cudaSetDevice(current);
+   solid_gpu_finalize();
+}
+
+// ---------------------------------------------------------------------------------- unary
+#define OCGPU_DEFINE_UNARY(OP, SOLID)                                                              \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *src, const OcTensorView *dst)                  \
+{                                                                                                  \
+   if (check_elemwise(src, "source") != 0 || check_elemwise(dst, "destination") != 0) return -1;   \
+   if (!same_shape(src, dst)) return fail("Tensor size mismatch in " #OP);                         \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   if (f == nullptr) return -1;                                                                    \
+   if (set_device(dst->device) != 0) return -1;                                                    \
+   if (start_read(dst, src) != 0) return -1;                                                       \
+   if (f(src->ndims, src->size, src->strides, src->data, dst->strides, dst->data, dst->stream) != 0) return fail_solid(); \
+   if (update(dst) != 0) return -1;                                                                \
+   return finish_read(dst, src);                                                                   \
+}
+OCGPU_UNARY_OPS(OCGPU_DEFINE_UNARY)
+
+// ---------------------------------------------------------------------------------- binary
+#define OCGPU_DEFINE_BINARY(OP, SOLID)                                                             \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *src1, const OcTensorView *src2, const OcTensorView *dst) \
+{                                                                                                  \
+   if (check_elemwise(src1, "first source") != 0 || check_elemwise(src2, "second source") != 0 ||  \
+       check_elemwise(dst, "destination") != 0) return -1;                                         \
+   if (!same_shape(src1, dst) || !same_shape(src2, dst)) return fail("Tensor size mismatch in " #OP); \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src1->dtype, #OP);                       \
+   if (f == nullptr) return -1;                                                                    \
+   if (set_device(dst->device) != 0) return -1;                                                    \
+   if (start_read(dst, src1) != 0 || start_read(dst, src2) != 0) return -1;                        \
+   if (f(dst->ndims, dst->size, src1->strides, src1->data, src2->strides, src2->data,              \
+         dst->strides, dst->data, dst->stream) != 0) return fail_solid();                          \
+   if (update(dst) != 0) return -1;                                                                \
+   if (finish_read(dst, src2) != 0) return -1;                                                     \
+   return finish_read(dst, src1);                                                                  \
+}
+OCGPU_BINARY_OPS(OCGPU_DEFINE_BINARY)
+
+// ---------------------------------------------------------------------------------- copy / fill
+extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst)
+{
+   if (check_view(src, "source") != 0 || check_view(dst, "destination") != 0) return -1;
+   size_t n1 = 1, n2 = 1;
+   for (int i = 0; i < src->ndims; i++) n1 *= src->size[i];
+   for (int i = 0; i < dst->ndims; i++) n2 *= dst->size[i];
+   if (n1 != n2) return fail("Mismatch in number of elements in tensor copy");
+   if (set_device(dst->device) != 0) return -1;
+   if (start_read(dst, src) != 0) return -1;
+   const int flags = (src->byteswapped ? SOLID_GPU_COPY_SRC_SWAPPED : 0) | (dst->byteswapped ? SOLID_GPU_COPY_DST_SWAPPED : 0);
+   if (src->device == dst->device) {
+      if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, src->ndims, src->size, src->strides, src->data,
+                            dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+   } else {
+      // other device: gather into a dense buffer of the source type on the source device, move it
+      // with one peer copy, convert on the destination (OcTensor_intrnlCopyDevices, tensor_itf.c:895-1041)
+      const size_t bytes = n1 * (size_t)solid_gpu_type_size[src->dtype];
+      void *tmp_src = nullptr, *tmp_dst = nullptr;
+      size_t dense[1] = { n1 }; ptrdiff_t step[1] = { solid_gpu_type_size[src->dtype] };
+      if (set_device(src->device) != 0 || temporary(src->device, bytes, &tmp_src) != 0) return -1;
+      if (solid_gpu_copy_ex(src->dtype, src->dtype, 0, src->ndims, src->size, src->strides, src->data,
+                            1, dense, step, tmp_src, src->stream) != 0) return fail_solid();
+      cudaEvent_t ev;
+      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
+      cudaEventRecord(ev, src->stream);
+      if (set_device(dst->device) != 0 || temporary(dst->device, bytes, &tmp_dst) != 0) { cudaEventDestroy(ev); return -1; }
+      cudaStreamWaitEvent(dst->stream, ev, 0);
+      cudaEventDestroy(ev);
+      cudaError_t st = cudaMemcpyPeerAsync(tmp_dst, dst->device, tmp_src, src->device, bytes, dst->stream);
+      if (st != cudaSuccess) return fail_cuda(st, "Error copying between devices");
+      if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, 1, dense, step, tmp_dst,
+                            dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+   }
+   if (update(dst) != 0) return -1;
+   return finish_read(dst, src);
+}
+
+extern "C" int OcTensorGPU_byteswapNoFlag(const OcTensorView *t)
+{
+   if (check_view(t, "input") != 0) return -1;
+   solid_funptr_gpu_byteswap f = lookup(solid_gpu_byteswap, t->dtype, "byteswap");
+   if (f == nullptr || set_device(t->device) != 0) return -1;
+   if (f(t->ndims, t->size, t->strides, t->data, t->stream) != 0) return fail_solid();
+   return update(t);
+}
+
+static int fill_common(const OcTensorView *t, const OcScalarView *s, solid_funptr_gpu_fill const *table, const char *desc)
+{
+   if (check_elemwise(t, "destination") != 0) return -1;
+   if (s == nullptr || s->dtype != t->dtype) return fail("The scalar must have the data type of the tensor");
+   solid_funptr_gpu_fill f = lookup(table, t->dtype, desc);
+   if (f == nullptr || set_device(t->device) != 0) return -1;
+   if (f(t->ndims, t->size, t->strides, t->data, s->value, t->stream) != 0) return fail_solid();
+   return update(t);
+}
+extern "C" int OcTensorGPU_fill(const OcTensorView *t, const OcScalarView *s) { return fill_common(t, s, solid_gpu_fill, "fill"); }
+extern "C" int OcTensorGPU_fillNaN(const OcTensorView *t, const OcScalarView *s) { return fill_common(t, s, solid_gpu_fill_nan, "fillNaN"); }
+
+extern "C" int OcTensorGPU_maskedFill(const OcTensorView *t, const OcTensorView *mask, const OcScalarView *s)
+{
+   if (check_elemwise(t, "destination") != 0 || check_elemwise(mask, "mask") != 0) return -1;
+   if (mask->dtype != SD_BOOL) return fail("The mask must have type bool");
+   if (!same_shape(t, mask)) return fail("Tensor size mismatch in maskedFill");
+   if (s == nullptr || s->dtype != t->dtype) return fail("The scalar must have the data type of the tensor");
+   solid_funptr_gpu_masked_fill f = lookup(solid_gpu_masked_fill, t->dtype, "maskedFill");
+   if (f == nullptr || set_device(t->device) != 0) return -1;
+   if (start_read(t, mask) != 0) return -1;
+   if (f(t->ndims, t->size, t->strides, t->data, mask->strides, mask->data, s->value, t->stream) != 0) return fail_solid();
+   if (update(t) != 0) return -1;
+   return finish_read(t, mask);
+}
+
+// ---------------------------------------------------------------------------------- global reductions
+namespace {
+struct ReduceSetup { void *buffer; };
+int reduce_begin(const OcTensorView *t, ReduceSetup *rs)             // OcTensorGPU_intrnlInitializeReduce
+{
+   if (check_elemwise(t, "input") != 0) return -1;
+   if (set_device(t->device) != 0) return -1;
+   size_t n = 1, bytes = 0;
+   for (int i = 0; i < t->ndims; i++) n *= t->size[i];
+   if (solid_gpu_reduce_all_buffer_size(n, t->device, &bytes) != 0) return fail_solid();
+   return temporary(t->device, bytes, &rs->buffer);
+}
+} // namespace
+
+#define OCGPU_DEFINE_RBOOL(OP, SOLID)                                                              \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, int *result)                                \
+{                                                                                                  \
+   ReduceSetup rs; solid_bool value = 0;                                                           \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   if (f(t->ndims, t->size, t->strides, t->data, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   *result = value ? 1 : 0;                                                                        \
+   return 0;                                                                                       \
+}
+OCGPU_REDUCE_BOOL_OPS(OCGPU_DEFINE_RBOOL)
+
+#define OCGPU_DEFINE_RSCALAR(OP, SOLID)                                                            \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, OcScalarView *result)                       \
+{                                                                                                  \
+   ReduceSetup rs;                                                                                 \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   memset(&result->value, 0, sizeof(result->value));                                               \
+   result->dtype = OcGPU_reductionResultType(#SOLID, t->dtype);                                    \
+   if (f(t->ndims, t->size, t->strides, t->data, &result->value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   return 0;                                                                                       \
+}
+OCGPU_REDUCE_SCALAR_OPS(OCGPU_DEFINE_RSCALAR)
+
+#define OCGPU_DEFINE_RNNZ(OP, SOLID)                                                               \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, solid_uint64 *result)                       \
+{                                                                                                  \
+   ReduceSetup rs;                                                                                 \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   if (f(t->ndims, t->size, t->strides, t->data, result, rs.buffer, t->stream) != 0) return fail_solid(); \
+   return 0;                                                                                       \
+}
+OCGPU_DEFINE_RNNZ(nnz, nnz) OCGPU_DEFINE_RNNZ(nnzNaN, nnz_nan)
+
+#define OCGPU_DEFINE_RNORM(OP, SOLID)                                                              \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, double p, OcScalarView *result)             \
+{                                                                                                  \
+   ReduceSetup rs;                                                                                 \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   memset(&result->value, 0, sizeof(result->value));                                               \
+   result->dtype = OcGPU_reductionResultType(#SOLID, t->dtype);                                    \
+   if (f(t->ndims, t->size, t->strides, t->data, p, &result->value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   return 0;                                                                                       \
+}
+OCGPU_DEFINE_RNORM(norm, norm) OCGPU_DEFINE_RNORM(normNaN, norm_nan)
+
+#define OCGPU_DEFINE_BOUND1(OP, SOLID)                                                             \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, const OcScalarView *bound, int *result)     \
+{                                                                                                  \
+   ReduceSetup rs; solid_bool value = 0;                                                           \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   if (bound == nullptr || bound->dtype != t->dtype) return fail("The bound must have the data type of the tensor"); \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   solid_scalar b = bound->value;                                                                  \
+   if (f(t->ndims, t->size, t->strides, t->data, &b, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   *result = value ? 1 : 0;                                                                        \
+   return 0;                                                                                       \
+}
+OCGPU_DEFINE_BOUND1(allLT, all_lt) OCGPU_DEFINE_BOUND1(allLE, all_le) OCGPU_DEFINE_BOUND1(allGT, all_gt) OCGPU_DEFINE_BOUND1(allGE, all_ge)
+
+#define OCGPU_DEFINE_BOUND2(OP, SOLID)                                                             \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *t, const OcScalarView *lower, const OcScalarView *upper, int *result) \
+{                                                                                                  \
+   ReduceSetup rs; solid_bool value = 0;                                                           \
+   if (reduce_begin(t, &rs) != 0) return -1;                                                       \
+   if (lower == nullptr || upper == nullptr || lower->dtype != t->dtype || upper->dtype != t->dtype) \
+      return fail("The bounds must have the data type of the tensor");                             \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
+   if (f == nullptr) return -1;                                                                    \
+   solid_scalar lo = lower->value, hi = upper->value;                                              \
+   if (f(t->ndims, t->size, t->strides, t->data, &lo, &hi, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   *result = value ? 1 : 0;                                                                        \
+   return 0;                                                                                       \
+}
+OCGPU_DEFINE_BOUND2(allGTLT, all_gtlt) OCGPU_DEFINE_BOUND2(allGTLE, all_gtle)
+OCGPU_DEFINE_BOUND2(allGELT, all_gelt) OCGPU_DEFINE_BOUND2(allGELE, all_gele)
+
+// ---------------------------------------------------------------------------------- axis reductions
+namespace {
+// Split src into kept and reduced dimensions, plan, fetch scratch (OcTensorGPU_intrnlAxisReduce,
+// tensor_reduce_axis_gpu.c:127-158).
+int axis_begin(const OcTensorView *src, int n, const int *axes, const OcTensorView *dst, const char *solid_name,
+               solid_gpu_reduce_axis_config *config)
+{
+   if (check_elemwise(src, "source") != 0 || check_elemwise(dst, "destination") != 0) return -1;
+   bool reduced[SOLID_MAX_TENSOR_DIMS] = { false };
+   for (int i = 0; i < n; i++) {
+      if (axes[i] < 0 || axes[i] >= src->ndims) return fail("Axis index %d out of range", axes[i]);
+      if (reduced[axes[i]]) return fail("Duplicate axis %d", axes[i]);
+      reduced[axes[i]] = true;
+   }
+   size_t size[SOLID_MAX_TENSOR_DIMS], rsize[SOLID_MAX_TENSOR_DIMS];
+   ptrdiff_t st1[SOLID_MAX_TENSOR_DIMS], st2[SOLID_MAX_TENSOR_DIMS], rst[SOLID_MAX_TENSOR_DIMS];
+   int nd = 0, rd = 0;
+   for (int i = 0; i < src->ndims; i++) {
+      if (reduced[i]) { rsize[rd] = src->size[i]; rst[rd] = src->strides[i]; rd++; }
+      else { size[nd] = src->size[i]; st1[nd] = src->strides[i]; nd++; }
+   }
+   // the destination either drops the reduced dimensions or keeps them with extent one
+   int j = 0;
+   if (dst->ndims == nd) { for (int i = 0; i < nd; i++) st2[i] = dst->strides[i]; }
+   else if (dst->ndims == src->ndims) { for (int i = 0; i < src->ndims; i++) if (!reduced[i]) st2[j++] = dst->strides[i]; }
+   else return fail("Destination dimensions do not match the reduction");
+   j = 0;
+   for (int i = 0; i < dst->ndims; i++) {
+      size_t expect = (dst->ndims == nd) ? size[i] : (reduced[i] ? 1 : src->size[i]);
+      if (dst->size[i] != expect) return fail("Destination size mismatch in axis reduction");
+   }
+   int rtype = OcGPU_reductionResultType(solid_name, src->dtype);
+   if (dst->dtype != rtype) return fail("The destination must have type %s", rtype >= 0 ? dtype_names[rtype] : "?");
+   if (set_device(dst->device) != 0) return -1;
+   if (solid_gpu_reduce_axis_prepare(config, solid_gpu_worktype_size[rtype], nd, size, st1, src->data, st2, dst->data,
+                                     rd, rsize, rst, dst->stream) != 0) return fail_solid();
+   if (config->bufferSize > 0) {
+      void *buf = nullptr;
+      if (temporary(dst->device, config->bufferSize, &buf) != 0) return -1;
+      config->data.ptrBuffer = (char *)buf;
+   }
+   return start_read(dst, src);
+}
+} // namespace
+
+#define OCGPU_DEFINE_AXIS(OP, SOLID)                                                               \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *src, int n, const int *axes, const OcTensorView *dst) \
+{                                                                                                  \
+   solid_gpu_reduce_axis_config config;                                                            \
+   if (axis_begin(src, n, axes, dst, #SOLID, &config) != 0) return -1;                             \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   if (f == nullptr) return -1;                                                                    \
+   if (f(&config) != 0) return fail_solid();                                                       \
+   if (update(dst) != 0) return -1;                                                                \
+   return finish_read(dst, src);                                                                   \
+}
+OCGPU_AXIS_OPS(OCGPU_DEFINE_AXIS)
+
+#define OCGPU_DEFINE_AXIS_NORM(OP, SOLID)                                                          \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *src, double p, int n, const int *axes, const OcTensorView *dst) \
+{                                                                                                  \
+   solid_gpu_reduce_axis_config config;                                                            \
+   if (axis_begin(src, n, axes, dst, #SOLID, &config) != 0) return -1;                             \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   if (f == nullptr) return -1;                                                                    \
+   if (f(&config, p) != 0) return fail_solid();                                                    \
+   if (update(dst) != 0) return -1;                                                                \
+   return finish_read(dst, src);                                                                   \
+}
+OCGPU_DEFINE_AXIS_NORM(axisNorm, axis_norm) OCGPU_DEFINE_AXIS_NORM(axisNormNaN, axis_norm_nan)

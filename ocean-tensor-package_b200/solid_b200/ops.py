@@ -18,6 +18,7 @@ import struct
 import numpy as np
 
 from . import _lib
+from . import _ocean
 from . import dtypes as dt
 from . import oplist as ol
 from .tensor import Tensor
@@ -32,6 +33,20 @@ def _lib_for(t: Tensor):
     import torch
     torch.cuda.set_device(t.storage.device)              # Solid reads launch parameters from the current device
     return _lib.get()
+
+
+def _dispatch(name: str, *args):
+    """Call OcTensorGPU_<name> of the Ocean-level dispatch library; tensors become views on the
+    current torch stream of their device."""
+    import ctypes as C
+    oc = _ocean.get()
+    conv, keep = [], []
+    for a in args:
+        if isinstance(a, Tensor):
+            v = oc.view(a, _stream(a)); keep.append(v); conv.append(C.byref(v))
+        else:
+            conv.append(a)
+    oc._check(oc.fn(name)(*conv), name)
 
 
 def scalar_bytes(value, dtype: str) -> bytes:
@@ -75,10 +90,7 @@ def _half_bits(x: float) -> np.ndarray:
 # ---------------------------------------------------------------------------
 def copy(src: Tensor, dst: Tensor) -> Tensor:
     """dst[...] = src with type conversion, byte-order handling and any alignment."""
-    lib = _lib_for(dst)
-    flags = (1 if src.byteswapped else 0) | (2 if dst.byteswapped else 0)
-    lib.copy_ex(src.dtype, dst.dtype, flags, src.size, src.strides, src.ptr, dst.size, dst.strides, dst.ptr,
-                _stream(dst))
+    _dispatch("copy", src, dst)
     return dst
 
 
@@ -92,24 +104,30 @@ def clone(src: Tensor) -> Tensor:
 
 def byteswap(t: Tensor) -> Tensor:
     """Reverse the stored bytes in place and flip the flag, so the logical values are unchanged."""
-    _lib_for(t).byteswap(t.dtype, t.size, t.strides, t.ptr, _stream(t))
+    _dispatch("byteswapNoFlag", t)
     t.byteswapped = not t.byteswapped
     return t
 
 
 def fill(t: Tensor, value) -> Tensor:
-    _lib_for(t).fill("fill", t.dtype, t.size, t.strides, t.ptr, scalar_bytes(value, t.dtype), _stream(t))
+    import ctypes as C
+    sv = _ocean.get().scalar(scalar_bytes(value, t.dtype), t.dtype)
+    _dispatch("fill", t, C.byref(sv))
     return t
 
 
 def fill_nan(t: Tensor, value) -> Tensor:
-    _lib_for(t).fill("fill_nan", t.dtype, t.size, t.strides, t.ptr, scalar_bytes(value, t.dtype), _stream(t))
+    import ctypes as C
+    sv = _ocean.get().scalar(scalar_bytes(value, t.dtype), t.dtype)
+    _dispatch("fillNaN", t, C.byref(sv))
     return t
 
 
 def masked_fill(t: Tensor, mask: Tensor, value) -> Tensor:
+    import ctypes as C
     m = mask.broadcast_to(t.size)
-    _lib_for(t).masked_fill(t.dtype, t.size, t.strides, t.ptr, m.strides, m.ptr, scalar_bytes(value, t.dtype), _stream(t))
+    sv = _ocean.get().scalar(scalar_bytes(value, t.dtype), t.dtype)
+    _dispatch("maskedFill", t, m, C.byref(sv))
     return t
 
 
@@ -179,7 +197,7 @@ def unary(name: str, src: Tensor, dst: Tensor | None = None) -> Tensor:
     else:
         rtype = src.dtype
     out = dst if (dst is not None and dst.dtype == rtype and not dst.byteswapped) else Tensor.empty(src.size, rtype, src.storage.device)
-    _lib_for(out).unary(name, x.dtype, x.size, x.strides, x.ptr, out.strides, out.ptr, _stream(out))
+    _dispatch(_ocean.ocean_name(name), x, out)
     if dst is not None and out is not dst:
         copy(out, dst)
         return dst
@@ -205,7 +223,7 @@ def binary(name: str, a: Tensor, b: Tensor, dst: Tensor | None = None) -> Tensor
     rtype = "bool" if name in ol.COMPARE_OPS else ctype
     out = dst if (dst is not None and dst.dtype == rtype and not dst.byteswapped and dst.size == size) \
         else Tensor.empty(size, rtype, a.storage.device)
-    _lib_for(out).binary(name, ctype, size, x.strides, x.ptr, y.strides, y.ptr, out.strides, out.ptr, _stream(out))
+    _dispatch(_ocean.ocean_name(name), x, y, out)
     if dst is not None and out is not dst:
         copy(out, dst)
         return dst
@@ -281,29 +299,47 @@ def _native(t: Tensor) -> Tensor:
 
 def reduce_all(name: str, t: Tensor, bounds=(), p=None):
     """Global reduction; returns a numpy scalar of the result type (on the host, like Ocean)."""
+    import ctypes as C
     t = _native(t)
-    lib = _lib_for(t)
-    buf = _scratch_buffer(t.storage.device, lib.reduce_all_buffer_size(max(t.nelem, 1), t.device_index))
-    raw = lib.reduce_all(name, t.dtype, t.size, t.strides, t.ptr, buf.data_ptr(), _stream(t),
-                         bounds=[scalar_bytes(b, t.dtype) for b in bounds], p=p)
-    rtype = ol.reduce_result_type(name, t.dtype)
+    oc = _ocean.get()
+    oname = _ocean.ocean_name(name)
+    if name in ol.REDUCE_BOOL_OPS:
+        r = C.c_int(0)
+        _dispatch(oname, t, C.byref(r))
+        return np.uint8(r.value)
+    if name in ol.REDUCE_BOUND1_OPS or name in ol.REDUCE_BOUND2_OPS:
+        r = C.c_int(0)
+        sv = [oc.scalar(scalar_bytes(b, t.dtype), t.dtype) for b in bounds]
+        _dispatch(oname, t, *[C.byref(v) for v in sv], C.byref(r))
+        return np.uint8(r.value)
+    if name in ol.REDUCE_U64_OPS:
+        r = C.c_uint64(0)
+        _dispatch(oname, t, C.byref(r))
+        return np.uint64(r.value)
+    res = _ocean.ScalarView()
+    if name in ol.REDUCE_NORM_OPS:
+        _dispatch(oname, t, C.c_double(p), C.byref(res))
+    else:
+        _dispatch(oname, t, C.byref(res))
+    rtype = dt.NAMES[res.dtype]
+    raw = bytes(C.string_at(C.addressof(res.value), 16))
     return np.frombuffer(raw[: dt.SIZE[rtype]], dtype=dt.NUMPY[rtype])[0]
 
 
 def reduce_axis(name: str, t: Tensor, axes, dst: Tensor | None = None, p=None, keepdims: bool = False) -> Tensor:
+    import ctypes as C
     t = _native(t)
     axes = sorted({a % t.ndims for a in ([axes] if isinstance(axes, int) else axes)})
     keep = [i for i in range(t.ndims) if i not in axes]
     rtype = ol.reduce_result_type("axis_" + name, t.dtype)
     osize = [t.size[i] for i in keep]
     out = dst if dst is not None else Tensor.empty(osize, rtype, t.storage.device)
-    lib = _lib_for(t)
-    cfg = lib.reduce_axis_prepare(dt.WORKSIZE[rtype], osize, [t.strides[i] for i in keep], t.ptr,
-                                  out.strides[: len(osize)], out.ptr, [t.size[i] for i in axes],
-                                  [t.strides[i] for i in axes], _stream(t))
-    if cfg.bufferSize:
-        cfg.data.ptrBuffer = _scratch_buffer(t.storage.device, cfg.bufferSize).data_ptr()
-    lib.reduce_axis("axis_" + name, t.dtype, cfg, p=p)
+    ax = (C.c_int * max(len(axes), 1))(*axes)
+    oname = _ocean.ocean_name("axis_" + name)
+    if p is None:
+        _dispatch(oname, t, C.c_int(len(axes)), ax, out)
+    else:
+        _dispatch(oname, t, C.c_double(p), C.c_int(len(axes)), ax, out)
     if keepdims:
         size = [1 if i in axes else t.size[i] for i in range(t.ndims)]
         return Tensor(out.storage, out.dtype, size, None, out.offset)

@@ -1,0 +1,161 @@
+"""The Ocean-level dispatch library (include/ocean_gpu_b200.h): exported symbols, the error
+behaviour of the reference's dispatch functions (typed "not supported" errors from table holes,
+precondition checks) without a GPU, and on the GPU the stream protocol, the scratch cache and the
+host-scalar results."""
+import ctypes as C
+import re
+import subprocess
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+from solid_b200 import _ocean, dtypes as dt, oplist as ol
+from solid_b200._ocean import OceanError, TensorView
+
+ROOT = Path(__file__).resolve().parent.parent
+
+
+def fake_view(dtype="float", size=(4,), device=0, byteswapped=False):
+    v = TensorView()
+    v.dtype, v.ndims = dt.INDEX[dtype], len(size)
+    step = dt.SIZE[dtype]
+    for i, s in enumerate(size):
+        v.size[i], v.strides[i] = s, step
+        step *= s
+    v.data, v.device, v.byteswapped = 256, device, int(byteswapped)
+    return v
+
+
+def test_dispatch_library_exports_declared_functions():
+    out = subprocess.run(["gcc", "-E", "-P", "-I", str(ROOT / "include"), "-I", "/usr/local/cuda/include",
+                          str(ROOT / "include" / "ocean_gpu_b200.h")], stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert out.returncode == 0, out.stderr[-1500:]
+    names = set(re.findall(r"\b(OcTensorGPU_\w+|OcGPU_\w+|OcInitGPU_B200|OcFinalizeGPU_B200)\s*\(", out.stdout))
+    assert len(names) > 120
+    oc = _ocean.get()
+    missing = sorted(n for n in names if not hasattr(oc.dll, n))
+    assert not missing, missing
+    # every Solid operation of the path is reachable under its Ocean name
+    for fam in (ol.UNARY_OPS, ol.BINARY_OPS, ol.REDUCE_BOOL_OPS, ol.REDUCE_BOUND1_OPS, ol.REDUCE_BOUND2_OPS,
+                ol.REDUCE_U64_OPS, ol.REDUCE_VOID_OPS, ol.REDUCE_NORM_OPS, ol.AXIS_OPS, ol.AXIS_NORM_OPS):
+        for n in fam:
+            assert oc.has(_ocean.ocean_name(n)), n
+
+
+def test_name_mapping():
+    assert _ocean.ocean_name("multiply") == "scale"
+    assert _ocean.ocean_name("bitwise_not") == "bitwiseNot"
+    assert _ocean.ocean_name("true_divide") == "trueDivide"
+    assert _ocean.ocean_name("lt") == "elemwiseLT"
+    assert _ocean.ocean_name("sum_abs_nan") == "sumAbsNaN"
+    assert _ocean.ocean_name("all_gtle") == "allGTLE"
+    assert _ocean.ocean_name("axis_norm2_nan") == "axisNorm2NaN"
+    assert _ocean.ocean_name("any_inf") == "anyInf"
+
+
+def test_reduction_result_types_agree_with_python_table():
+    oc = _ocean.get()
+    for op in list(ol.REDUCE_BOOL_OPS) + list(ol.REDUCE_U64_OPS) + list(ol.REDUCE_VOID_OPS) + list(ol.REDUCE_NORM_OPS):
+        for t in dt.NAMES:
+            assert oc.result_type(op, t) == ol.reduce_result_type(op, t), (op, t)
+            assert oc.result_type("axis_" + op, t) == ol.reduce_result_type(op, t)
+
+
+def test_errors_before_any_cuda_call():
+    oc = _ocean.get()
+    a, b, d = fake_view("float"), fake_view("float"), fake_view("float")
+    with pytest.raises(OceanError, match="not supported for type bool"):
+        vb = fake_view("bool")
+        oc._check(oc.fn("sin")(C.byref(vb), C.byref(vb)), "sin")
+    with pytest.raises(OceanError, match="not supported for type float"):
+        oc._check(oc.fn("bitwiseAnd")(C.byref(a), C.byref(b), C.byref(d)), "bitwiseAnd")
+    with pytest.raises(OceanError, match="not supported for type complex-double"):
+        vc = fake_view("cdouble")
+        oc._check(oc.fn("floorDivide")(C.byref(vc), C.byref(vc), C.byref(vc)), "floorDivide")
+    with pytest.raises(OceanError, match="size mismatch"):
+        other = fake_view("float", (5,))
+        oc._check(oc.fn("add")(C.byref(a), C.byref(other), C.byref(d)), "add")
+    with pytest.raises(OceanError, match="native byte order"):
+        sw = fake_view("float", byteswapped=True)
+        oc._check(oc.fn("add")(C.byref(sw), C.byref(b), C.byref(d)), "add")
+    with pytest.raises(OceanError, match="number of elements"):
+        oc._check(oc.fn("copy")(C.byref(a), C.byref(fake_view("double", (3,)))), "copy")
+    with pytest.raises(OceanError, match="must have type"):
+        ax = (C.c_int * 1)(0)
+        m = fake_view("float", (4, 3)); o = fake_view("double", (3,))
+        oc._check(oc.fn("axisSum")(C.byref(m), C.c_int(1), ax, C.byref(o)), "axisSum")
+    with pytest.raises(OceanError, match="out of range"):
+        ax = (C.c_int * 1)(7)
+        m = fake_view("float", (4, 3)); o = fake_view("float", (3,))
+        oc._check(oc.fn("axisSum")(C.byref(m), C.c_int(1), ax, C.byref(o)), "axisSum")
+    with pytest.raises(OceanError, match="data type of the tensor"):
+        sv = oc.scalar(b"\0" * 8, "double")
+        oc._check(oc.fn("fill")(C.byref(a), C.byref(sv)), "fill")
+
+
+# ------------------------------------------------------------------------------------ GPU
+@pytest.mark.gpu
+def test_results_and_scratch_cache_rotation(gpu):
+    """Many host-returning reductions in a row (the scratch cache has three slots) with sizes that
+    force the slots to grow, checked against float64 sums."""
+    from solid_b200 import Tensor, ops
+    _ocean.get().init()
+    rng = np.random.default_rng(1)
+    for n in (10, 100000, 5, 3000000, 17, 1 << 22, 1000):
+        x = rng.uniform(-1, 1, n).astype(np.float32)
+        t = Tensor.from_numpy(x)
+        assert abs(float(ops.sum(t)) - x.astype(np.float64).sum()) <= 1e-5 * np.sqrt(n) * np.abs(x).sum()
+        assert ops.maximum(t) == x.max() and ops.nnz(t) == np.count_nonzero(x)
+        assert ops.all(t) == np.uint8(np.all(x != 0))
+        assert ops.reduce_all("all_gtlt", t, bounds=(-1.5, 1.5)) == 1
+        assert ops.reduce_all("all_lt", t, bounds=(0.0,)) == 0 or n < 20
+    m = rng.normal(size=(300, 200))
+    tm = Tensor.from_numpy(m)
+    assert np.allclose(ops.sum(tm, 0).numpy(), m.sum(axis=0), atol=1e-9)
+    assert np.allclose(ops.norm(tm, 3, [1]).numpy(), (np.abs(m) ** 3).sum(axis=1) ** (1 / 3), rtol=1e-5)
+
+
+@pytest.mark.gpu
+def test_stream_protocol_orders_producer_and_consumer(gpu):
+    """The source is produced on one stream, the operation runs on the destination's stream: the
+    dispatch must wait for the source's event, and record the destination's."""
+    import torch
+    from solid_b200 import Tensor
+    oc = _ocean.get()
+    n = 1 << 24
+    s1, s2 = torch.cuda.Stream(), torch.cuda.Stream()
+    e1 = torch.cuda.Event(); e2 = torch.cuda.Event()
+    a = Tensor.empty([n], "float"); b = Tensor.empty([n], "float"); c = Tensor.empty([n], "float")
+    torch.cuda.synchronize()
+    one = oc.scalar(np.float32(1.0).tobytes(), "float"); two = oc.scalar(np.float32(2.0).tobytes(), "float")
+    va = oc.view(a, s1.cuda_stream, e1.cuda_event if hasattr(e1, "cuda_event") else 0)
+    # torch events expose their handle only after a record; record once so the handle exists
+    with torch.cuda.stream(s1):
+        e1.record()
+    with torch.cuda.stream(s2):
+        e2.record()
+    va = oc.view(a, s1.cuda_stream, e1.cuda_event); vb = oc.view(b, s1.cuda_stream, e1.cuda_event)
+    vc = oc.view(c, s2.cuda_stream, e2.cuda_event)
+    for _ in range(5):                                        # producers on stream 1
+        oc._check(oc.fn("fill")(C.byref(va), C.byref(one)), "fill")
+        oc._check(oc.fn("fill")(C.byref(vb), C.byref(two)), "fill")
+    oc._check(oc.fn("add")(C.byref(va), C.byref(vb), C.byref(vc)), "add")      # consumer on stream 2
+    e2.synchronize()                                         # the destination's event was recorded by the dispatch
+    got = c.storage[: 4 * n].cpu().numpy().view(np.float32)
+    assert np.all(got == 3.0)
+    torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_copy_between_devices(gpu):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    from solid_b200 import Tensor, ops
+    x = np.arange(100000, dtype=np.int32)
+    src = Tensor.from_numpy(x, device="cuda:0")
+    dst = Tensor.empty([100000], "double", device="cuda:1")
+    ops.copy(src.slice(0, 99999, -1, -1), dst)               # reversed, converted, other device
+    torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+    assert np.array_equal(dst.numpy(), x[::-1].astype(np.float64))
