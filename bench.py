@@ -199,18 +199,39 @@ def run_reference(args):
 # ---------------------------------------------------------------------------
 # per-operation table (configurations 1-4), N = 1 only
 # ---------------------------------------------------------------------------
-def time_gpu(fn, iters: int, warmup: int = 3):
+def time_gpu(fn, iters: int, warmup: int = 3, queued: bool = True):
+    """Device seconds per call of `fn`.
+
+    With `queued` the calls are issued behind a kernel that idles for a few milliseconds, so that all of them sit
+    in the stream before the first one starts: the figure is then the device time of the operation, not the time the
+    Python caller needs to issue it (which is larger than the kernel for the 30-60 us operations of this table).
+    Calls that wait for the device themselves (global reductions that return a host value) must pass queued=False.
+    """
     import torch
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if queued:
+        torch.cuda._sleep(int(2.0e6 * (2 + 0.25 * iters)))          # about 1 ms per 2e6 cycles
     start.record()
     for _ in range(iters):
         fn()
     stop.record()
     torch.cuda.synchronize()
     return start.elapsed_time(stop) / iters * 1e-3
+
+
+def time_call(fn, iters: int):
+    """Wall seconds per call of `fn` as the Python caller sees it (issue cost; the device may lag behind)."""
+    import torch
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    for _ in range(iters):
+        fn()
+    t1 = time.perf_counter()
+    torch.cuda.synchronize()
+    return (t1 - t0) / iters
 
 
 def ops_table(peak: float, with_cpu: bool):
@@ -226,10 +247,11 @@ def ops_table(peak: float, with_cpu: bool):
         if ref.available():
             cpu = ref.get(); cpu.set_threads(os.cpu_count() or 1)
 
-    def add_row(config, name, nbytes, fn, cpu_fn=None, iters=20, rotate=1):
-        t = time_gpu(fn, iters)
+    def add_row(config, name, nbytes, fn, cpu_fn=None, iters=20, queued=True):
+        t = time_gpu(fn, iters, queued=queued)
         row = {"config": config, "op": name, "bytes": nbytes, "us": t * 1e6, "gbs": nbytes / t / 1e9,
-               "frac_measured": nbytes / t / 1e9 / peak, "frac_8tbs": nbytes / t / 1e9 / NOMINAL_HBM_GBS}
+               "frac_measured": nbytes / t / 1e9 / peak, "frac_8tbs": nbytes / t / 1e9 / NOMINAL_HBM_GBS,
+               "issue_us": time_call(fn, iters) * 1e6}
         if cpu is not None and cpu_fn is not None:
             tc = min(time_cpu(cpu_fn, 3, 1))
             row["cpu_gbs"] = nbytes / tc / 1e9
@@ -257,7 +279,14 @@ def ops_table(peak: float, with_cpu: bool):
     for name in ("sum", "norm2", "maximum"):
         add_row("C1", name + " f32 2^24 (incl. host read-back)", 4 * n,
                 lambda name=name: ops.reduce_all(name, xs[rot()]),
-                (lambda name=name: cpu.reduce_all(name, "float", [n], [4], hx[0].ctypes.data)) if cpu else None)
+                (lambda name=name: cpu.reduce_all(name, "float", [n], [4], hx[0].ctypes.data)) if cpu else None, queued=False)
+    rbuf = torch.empty(lib.reduce_all_buffer_size(1 << 26, 0), dtype=torch.uint8, device="cuda")
+    rres = torch.empty(16, dtype=torch.uint8, device="cuda")
+    cur = torch.cuda.current_stream().cuda_stream
+    for name in ("sum", "norm2", "maximum"):
+        add_row("C1", name + " f32 2^24 (result stays on the device)", 4 * n,
+                lambda name=name: (lambda i: lib.reduce_all_device(name, "float", [n], [4], xs[i].ptr, rres.data_ptr(),
+                                                                   rbuf.data_ptr(), cur))(rot()))
 
     # ---- C2: C(f32) = A(f64, transposed) * B(i32, byteswapped) + r(f32 row broadcast), 4096^2; unaligned byteswapped f64 -> f16
     m = 4096
@@ -302,7 +331,9 @@ def ops_table(peak: float, with_cpu: bool):
     tb = dev(hb, "bool")
     for name in ("any", "all", "nnz"):
         add_row("C3", "%s bool 8192^2 (incl. host read-back)" % name, k * k, lambda name=name: ops.reduce_all(name, tb),
-                (lambda name=name: cpu.reduce_all(name, "bool", [k * k], [1], hb.ctypes.data)) if cpu else None)
+                (lambda name=name: cpu.reduce_all(name, "bool", [k * k], [1], hb.ctypes.data)) if cpu else None, queued=False)
+        add_row("C3", "%s bool 8192^2 (result stays on the device)" % name, k * k,
+                lambda name=name: lib.reduce_all_device(name, "bool", [k * k], [1], tb.ptr, rres.data_ptr(), rbuf.data_ptr(), cur))
     del tb
 
     # ---- C4: unary chain on 2^26 elements
@@ -376,7 +407,7 @@ def run_ours(args):
     def step(i=None):
         if i is not None:
             kstart[i].record()
-        ops.axpy_sums(0.5, tx, ty, tz, sums)                 # 2 launches: streaming kernel + fixed-order finish
+        ops.axpy_sums(0.5, tx, ty, tz, sums)                 # streaming kernel + one or two fixed-order folds
         if i is not None:
             kstop[i].record()
         if world > 1:
@@ -491,7 +522,8 @@ def run_ours(args):
             "e2e": {"value": BYTES_PER_ELEMENT * n_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
                     "note": "per rank; inputs streamed through 256 MiB pinned windows (double buffered), z stays on the device"},
-            "gpu_launches": 2 * args.steps * world,
+            # streaming kernel, fold of the per-block partials (two levels beyond 4096 blocks of 4096 floats)
+            "gpu_launches": (3 if -(-per // 4096) > 4096 else 2) * args.steps * world,
             "clocks": cl,
         }
         if world == 1 and not args.no_cpu:

@@ -292,14 +292,15 @@ SOLID_TYPES_real(SOLID_GPU_DECLARE_FN_, axpy)
 #undef SOLID_GPU_ARGS_CURRENT_
 
 /* z = a*x + y over n contiguous elements together with sum(z) and sum(z*z) in one pass.    */
-/* `partials` (device, solid_gpu_axpy_sums_buffer_size() bytes) receives the per-block      */
-/* partial sums; `sums` (device, 2 elements) receives { sum(z), sum(z*z) } combined in a    */
-/* fixed order by a second kernel, so that a collective can add the pairs of several GPUs   */
-/* before the square root is taken.  Nothing is copied to the host.  float and double.      */
+/* `partials` (device, solid_gpu_axpy_sums_buffer_size(device, n) bytes: one pair per 16 KB */
+/* of x, 8 MiB for 2^32 floats) receives the per-block partial sums; `sums` (device, 2      */
+/* elements) receives { sum(z), sum(z*z) } folded in a fixed order by one or two small      */
+/* kernels, so that a collective can add the pairs of several GPUs before the square root   */
+/* is taken.  Nothing is copied to the host.  float and double.                             */
 #define SOLID_GPU_ARGS_AXPY_SUMS \
    size_t n, const solid_scalar a, const void *x, const void *y, void *z, \
    void *sums, void *partials, cudaStream_t stream
-SOLID_API int solid_gpu_axpy_sums_buffer_size(int device, size_t *size);
+SOLID_API int solid_gpu_axpy_sums_buffer_size(int device, size_t n, size_t *size);
 SOLID_API int solid_gpu_axpy_sums_float(SOLID_GPU_ARGS_AXPY_SUMS);
 SOLID_API int solid_gpu_axpy_sums_double(SOLID_GPU_ARGS_AXPY_SUMS);
 

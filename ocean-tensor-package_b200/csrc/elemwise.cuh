@@ -262,7 +262,11 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
 inline int ew_grid(uint64_t work_items, uint64_t items_per_block, const DeviceInfo &dev)
 {
    uint64_t blocks = (work_items + items_per_block - 1) / items_per_block;
-   uint64_t cap = (uint64_t)dev.sms * (dev.max_threads_per_sm / EW_THREADS) * 4;   // a few waves, whole SM multiples
+   // One chunk per block: on B200 a streaming kernel launched this way measured 7.1 TB/s against 6.4-6.6 TB/s
+   // for a grid of one to four waves whose blocks stride through the arrays.  The loops in the kernels remain for
+   // tensors beyond the grid limit.
+   (void)dev;
+   const uint64_t cap = 0x7FFFFFFFull;
    if (blocks > cap) blocks = cap;
    if (blocks < 1) blocks = 1;
    return (int)blocks;

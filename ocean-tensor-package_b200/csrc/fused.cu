@@ -79,14 +79,23 @@ __global__ void __launch_bounds__(AX_THREADS) axpy_sums_kernel(uint64_t n, T a, 
    }
 }
 
-// Single block: thread t folds partials t, t+256, ... in order, then the block tree.
+// Fold of the per-block partials, in fixed order: block b takes partials [b*fold, (b+1)*fold), thread t
+// of it adds entries t, t+256, ... and the block tree joins the threads.  The streaming kernel runs one
+// chunk per block (measured on B200: 7.1 TB/s against 6.4 TB/s for a grid of resident blocks that
+// stride through the arrays), so a large tensor leaves up to a million partials; they are folded in two
+// levels, AX_FOLD to one and then the rest in a single block.
+constexpr int AX_FOLD = 4096;
+
 template <class T>
-__global__ void __launch_bounds__(AX_THREADS) axpy_sums_finish(int nparts, const Sums<T> *__restrict__ partials,
-                                                               T *__restrict__ sums)
+__global__ void __launch_bounds__(AX_THREADS) axpy_sums_finish(uint64_t nparts, int fold,
+                                                               const Sums<T> *__restrict__ partials,
+                                                               Sums<T> *__restrict__ out)
 {
    __shared__ Sums<T> smem[AX_THREADS / 32];
+   const uint64_t first = (uint64_t)blockIdx.x * fold;
+   uint64_t last = first + fold; if (last > nparts) last = nparts;
    T s = 0, s2 = 0;
-   for (int i = threadIdx.x; i < nparts; i += AX_THREADS) { s += partials[i].s; s2 += partials[i].s2; }
+   for (uint64_t i = first + threadIdx.x; i < last; i += AX_THREADS) { s += partials[i].s; s2 += partials[i].s2; }
 #pragma unroll
    for (int d = 16; d >= 1; d >>= 1) {
       s  += __shfl_down_sync(0xFFFFFFFFu, s, d);
@@ -97,11 +106,20 @@ __global__ void __launch_bounds__(AX_THREADS) axpy_sums_finish(int nparts, const
    __syncthreads();
    if (threadIdx.x == 0) {
       for (int w = 1; w < AX_THREADS / 32; w++) { s += smem[w].s; s2 += smem[w].s2; }
-      sums[0] = s; sums[1] = s2;
+      out[blockIdx.x].s = s; out[blockIdx.x].s2 = s2;
    }
 }
 
-static int axpy_sums_blocks(const DeviceInfo &dev) { return dev.sms * (dev.max_threads_per_sm / AX_THREADS); }
+// Blocks of the streaming kernel for n elements of `elemsize` bytes: one chunk each, within the grid limit.
+static uint64_t axpy_sums_blocks(uint64_t n, size_t elemsize)
+{
+   const uint64_t vec = 16 / elemsize, chunk = (uint64_t)AX_THREADS * 4 * vec;
+   uint64_t blocks = (n + chunk - 1) / chunk;
+   if (blocks < 1) blocks = 1;
+   if (blocks > 0x7FFFFFFFull) blocks = 0x7FFFFFFFull;
+   return blocks;
+}
+static uint64_t axpy_sums_level2(uint64_t blocks) { return blocks > (uint64_t)AX_FOLD ? (blocks + AX_FOLD - 1) / AX_FOLD : 0; }
 
 template <class T>
 int axpy_sums(size_t n, T a, const void *x, const void *y, void *z, void *sums, void *partials, cudaStream_t stream)
@@ -109,13 +127,17 @@ int axpy_sums(size_t n, T a, const void *x, const void *y, void *z, void *sums, 
    if (!aligned_to(x, 16) || !aligned_to(y, 16) || !aligned_to(z, 16))
       SD_ERROR("axpy_sums needs 16-byte aligned tensors");
    if (sums == nullptr || partials == nullptr) SD_ERROR("axpy_sums needs the sums and partials buffers");
-   DeviceInfo dev;
-   if (current_device_info(&dev) != 0) return -1;
-   const int blocks = axpy_sums_blocks(dev);
-   axpy_sums_kernel<T><<<blocks, AX_THREADS, 0, stream>>>((uint64_t)n, a, (const T *)x, (const T *)y, (T *)z,
-                                                        (Sums<T> *)partials);
+   const uint64_t blocks = axpy_sums_blocks((uint64_t)n, sizeof(T)), level2 = axpy_sums_level2(blocks);
+   Sums<T> *p1 = (Sums<T> *)partials, *p2 = p1 + blocks;
+   axpy_sums_kernel<T><<<(unsigned)blocks, AX_THREADS, 0, stream>>>((uint64_t)n, a, (const T *)x, (const T *)y, (T *)z, p1);
    SD_LAUNCH_CHECK();
-   axpy_sums_finish<T><<<1, AX_THREADS, 0, stream>>>(blocks, (const Sums<T> *)partials, (T *)sums);
+   if (level2) {
+      axpy_sums_finish<T><<<(unsigned)level2, AX_THREADS, 0, stream>>>(blocks, AX_FOLD, p1, p2);
+      SD_LAUNCH_CHECK();
+      axpy_sums_finish<T><<<1, AX_THREADS, 0, stream>>>(level2, (int)level2, p2, (Sums<T> *)sums);
+   } else {
+      axpy_sums_finish<T><<<1, AX_THREADS, 0, stream>>>(blocks, (int)blocks, p1, (Sums<T> *)sums);
+   }
    SD_LAUNCH_CHECK();
    return 0;
 }
@@ -471,11 +493,12 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
 
 } // namespace sd
 
-extern "C" int solid_gpu_axpy_sums_buffer_size(int device, size_t *size)
+extern "C" int solid_gpu_axpy_sums_buffer_size(int device, size_t n, size_t *size)
 {
-   solid_gpu_properties *prop = solid_gpu_get_device_properties(device);
-   if (prop == nullptr) return -1;
-   *size = (size_t)prop->multiprocessor_count * (prop->max_threads_per_multiprocessor / sd::AX_THREADS) * 16;
+   (void)device;                                  // the partial count depends on the length only
+   if (size == nullptr) { SD_ERROR("axpy_sums_buffer_size needs a result pointer"); }
+   const uint64_t blocks = sd::axpy_sums_blocks((uint64_t)n, sizeof(double));   // double has the most blocks
+   *size = (size_t)(blocks + sd::axpy_sums_level2(blocks)) * sizeof(sd::Sums<double>);
    return 0;
 }
 extern "C" int solid_gpu_axpy_sums_float(SOLID_GPU_ARGS_AXPY_SUMS)

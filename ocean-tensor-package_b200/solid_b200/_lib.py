@@ -200,9 +200,9 @@ class SolidGPU:
         self._check(self.fn("solid_gpu_axis_sum_float_noalloc")(C.byref(cfg)), "axis_sum_float_noalloc")
 
     # -- fused -----------------------------------------------------------------------
-    def axpy_sums_buffer_size(self, device: int) -> int:
+    def axpy_sums_buffer_size(self, device: int, n: int) -> int:
         out = C.c_size_t(0)
-        self._check(self.fn("solid_gpu_axpy_sums_buffer_size")(C.c_int(device), C.byref(out)), "axpy_sums_buffer_size")
+        self._check(self.fn("solid_gpu_axpy_sums_buffer_size")(C.c_int(device), C.c_size_t(n), C.byref(out)), "axpy_sums_buffer_size")
         return out.value
 
     def axpy_sums(self, dtype, n, a: bytes, x, y, z, sums, partials, stream=0):

@@ -388,6 +388,6 @@ def axpy_sums(a, x: Tensor, y: Tensor, z: Tensor | None = None, sums=None):
     tdt = torch.float32 if x.dtype == "float" else torch.float64
     if sums is None:
         sums = torch.empty(2, dtype=tdt, device=x.storage.device)
-    part = _scratch_buffer(x.storage.device, lib.axpy_sums_buffer_size(x.device_index))
+    part = _scratch_buffer(x.storage.device, lib.axpy_sums_buffer_size(x.device_index, x.nelem))
     lib.axpy_sums(x.dtype, x.nelem, scalar_bytes(a, x.dtype), x.ptr, y.ptr, z.ptr, sums.data_ptr(), part.data_ptr(), _stream(x))
     return z, sums

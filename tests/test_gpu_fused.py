@@ -111,8 +111,8 @@ def test_axpy_sums_matches_reference_sequence(dtype, gpu, cpu):
     dev = util.Device()
     rng = np.random.default_rng(9)
     es = dt.SIZE[dtype]
-    part = dev.empty(gpu.axpy_sums_buffer_size(0))
-    for n in (1, 5, 4096, 1000003):
+    for n in (1, 5, 4096, 1000003, (1 << 24) + 3):      # the last one needs the two-level fold of the partials
+        part = dev.empty(gpu.axpy_sums_buffer_size(0, n))
         x = rng.uniform(-1, 1, n).astype(dt.NUMPY[dtype]); y = rng.uniform(-1, 1, n).astype(dt.NUMPY[dtype])
         a = np.array([0.5], dtype=dt.NUMPY[dtype])
         t, z = np.zeros_like(x), np.zeros_like(x)
