@@ -10,6 +10,7 @@
 // identity (sum 0, prod 1, any 0, all 1) and are an error for minimum/maximum.
 // Not kept: the range tests read BOTH bounds (the reference's GPU wrapper copies
 // `lower` into `upper`, template_reduce_all.cu:208-209).
+#include <atomic>
 #include "reduce_unit.cuh"
 
 namespace sd {
@@ -19,9 +20,28 @@ extern thread_local void *reduce_all_device_result;
 // 64 pinned, device-mapped host bytes per device, created on first use (reduce_plan.cu).
 char *reduce_all_host_slot();
 
-template <class R> __global__ void red_identity(const R r, typename R::out_t *dst)
+template <class R> __global__ void red_identity(const R r, typename R::out_t *dst, const RedParams p)
 {
    if constexpr (!R::seeded) *dst = r.finalize(r.init());
+   red_signal(p);
+}
+
+// Wait until the finishing thread of the launch has set the slot's sequence word.  The value and the word
+// are written straight into mapped host memory, so a short poll sees them a few microseconds before a stream
+// synchronisation would return; after about a millisecond (long reductions, or a launch that failed and will
+// never write) the stream is synchronised instead, which also delivers the error.
+inline int reduce_all_wait(const char *host_slot, uint32_t seq, cudaStream_t stream)
+{
+   const volatile uint32_t *flag = reinterpret_cast<const volatile uint32_t *>(host_slot + 32);
+   for (int spin = 0; spin < 50000; spin++) {
+      if (*flag == seq) { std::atomic_thread_fence(std::memory_order_acquire); return 0; }
+#if defined(__x86_64__)
+      __builtin_ia32_pause();
+#endif
+   }
+   SD_CUDA_CHECK(cudaStreamSynchronize(stream));
+   if (*flag != seq) SD_ERROR("Global reduction finished without delivering its result");
+   return 0;
 }
 
 template <class R, class T>
@@ -44,9 +64,17 @@ int reduce_all(const R &r, const char *name, int ndims, const size_t *size, cons
    }
    p.dst = slot;
    p.buf = (char *)buffer + 16;
+   uint32_t sequence = 0;
+   if (host_slot != nullptr) {
+      uint32_t *counter = reinterpret_cast<uint32_t *>(host_slot + 48);   // host-only word: calls made through this slot
+      if (++*counter == 0) *counter = 1;                   // the slot starts out with 0 in its sequence word
+      sequence = *counter;
+      p.flag = reinterpret_cast<uint32_t *>(host_slot + 32);
+      p.flag_value = sequence;
+   }
    if (p.relem == 0) {
       if (R::seeded) SD_ERROR("The tensor %s function is undefined on empty tensors", name);
-      red_identity<R><<<1, 1, 0, stream>>>(r, reinterpret_cast<O *>(slot));
+      red_identity<R><<<1, 1, 0, stream>>>(r, reinterpret_cast<O *>(slot), p);
       SD_LAUNCH_CHECK();
    } else {
       DeviceInfo dev;
@@ -54,7 +82,7 @@ int reduce_all(const R &r, const char *name, int ndims, const size_t *size, cons
       if (red_launch<R, T>(r, p, red_split_cap(1, p.relem, dev.sms), stream) != 0) return -1;
    }
    if (host_slot == nullptr) return 0;
-   SD_CUDA_CHECK(cudaStreamSynchronize(stream));
+   if (reduce_all_wait(host_slot, sequence, stream) != 0) return -1;
    memcpy(result, host_slot, sizeof(O));
    return 0;
 }

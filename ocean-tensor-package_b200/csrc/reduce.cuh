@@ -30,6 +30,13 @@
 namespace sd {
 
 constexpr int RED_THREADS = 256;
+// Blocks per multiprocessor that a reduction aims for when it splits outputs over blocks: one resident
+// wave.  Measured on B200 (global and 8192^2 axis reductions), 16 or 32 per multiprocessor were slower.
+constexpr int RED_WANT_PER_SM = 8;
+// Resident blocks per multiprocessor asked of the compiler for the streaming kernels (64 registers per
+// thread: red_row always four); the 1- and 2-byte forms of red_col keep 16 or 8 accumulators per thread
+// and are left alone.
+#define RED_MIN_BLOCKS(T) (sizeof(T) >= 4 ? 4 : 1)
 
 struct RedParams {
    char    *src, *dst, *buf;
@@ -40,7 +47,15 @@ struct RedParams {
    uint32_t split;          // blocks (or groups) that share one output
    uint32_t group;          // red_row: threads per output chunk (32 or 256)
    uint64_t tiles0;         // red_col: tiles along outer dimension 0
+   unsigned int *ticket;    // single output split over blocks: arrival counter of the stream (the last block folds), or null
+   uint32_t *flag;          // host-returning form: word the finishing thread sets to flag_value after the result, or null
+   uint32_t flag_value;
 };
+
+// Arrival counter for single-pass folds on `stream` of the current device (reduce_plan.cu): one word
+// of a zero-initialised device array per stream, which the last block of a launch sets back to zero.
+// Null when no counter can be given (per-thread default stream, table full); callers then use red_fin.
+unsigned int *red_ticket_for_stream(cudaStream_t stream);
 
 // offset of output `o` in source (outer part) and destination
 SD_D void outer_offsets(const RedParams &p, uint64_t o, int64_t &off1, int64_t &off2)
@@ -101,12 +116,18 @@ template <class R, class T> SD_D typename R::acc_t red_start(const R &r, const c
    else { (void)first_elem; return r.init(); }
 }
 
+// Tell a polling host that the result is in place (the result itself lives in mapped host memory).
+SD_D void red_signal(const RedParams &p)
+{
+   if (p.flag) { __threadfence_system(); *reinterpret_cast<volatile uint32_t *>(p.flag) = p.flag_value; }
+}
+
 template <class R> SD_D void red_emit(const R &r, const RedParams &p, uint64_t out, uint32_t s,
                                       int64_t off2, const typename R::acc_t &acc)
 {
    using A = typename R::acc_t; using O = typename R::out_t;
    if (p.split > 1) reinterpret_cast<A *>(p.buf)[out * p.split + s] = acc;
-   else *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
+   else { *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc); red_signal(p); }
 }
 
 // Fold all VEC elements of one vector into the accumulator (packed-word form for 1-byte types
@@ -124,12 +145,69 @@ template <class R, class T, int VEC> SD_D void accum_vec(const R &r, typename R:
    }
 }
 
+// Second pass: a group of GROUP threads (one warp, or the whole block when an output has many
+// partials) folds the `split` partials of one output.  Thread l of the group takes partials
+// l, l+GROUP, ... in order; the threads are then joined by the shuffle tree and, for the block
+// form, by a fixed-order pass over the warps.  Threads without a partial are skipped, because
+// an extra copy of a partial is harmless only for idempotent folds.
+template <class R, class A> SD_D void fold_have(const R &r, A &acc, bool &have, uint32_t lane)
+{
+#pragma unroll
+   for (int d = 16; d >= 1; d >>= 1) {
+      A other = shfl_down_any<A>(acc, d);
+      bool other_has = __shfl_down_sync(0xFFFFFFFFu, (int)have, d) != 0 && (lane + d < 32);
+      if (other_has) { if (have) r.combine(acc, other); else { acc = other; have = true; } }
+   }
+}
+
+// Partials come from other multiprocessors: read them past the L1.
+template <class A> SD_D A load_partial(const A *q)
+{
+   if constexpr (sizeof(A) % 4 == 0) {
+      uint32_t w[sizeof(A) / 4];
+#pragma unroll
+      for (int i = 0; i < (int)(sizeof(A) / 4); i++) w[i] = __ldcg(reinterpret_cast<const uint32_t *>(q) + i);
+      A a; memcpy(&a, w, sizeof(A)); return a;
+   } else if constexpr (std::is_arithmetic<A>::value) {
+      return *reinterpret_cast<const volatile A *>(q);
+   } else {
+      return *q;
+   }
+}
+
+template <class R, int GROUP>
+SD_D void red_fin_body(const R &r, const RedParams &p, uint64_t out, bool live, typename R::acc_t *smem, int *shave)
+{
+   using A = typename R::acc_t; using O = typename R::out_t;
+   const uint32_t t = threadIdx.x % GROUP, lane = threadIdx.x & 31;
+   const A *part = reinterpret_cast<const A *>(p.buf) + (live ? out : 0) * p.split;
+   bool have = t < p.split;
+   A acc = load_partial(part + (have ? t : 0));
+   for (uint32_t i = t + GROUP; i < p.split; i += GROUP) r.combine(acc, load_partial(part + i));
+   fold_have(r, acc, have, lane);
+   if (GROUP > 32) {
+      const int warp = threadIdx.x >> 5;
+      if (lane == 0) { smem[warp] = acc; shave[warp] = have; }
+      __syncthreads();
+      if (threadIdx.x == 0)
+         for (int w = 1; w < RED_THREADS / 32; w++) if (shave[w]) r.combine(acc, smem[w]);   // warp 0 always has data
+   }
+   if (t == 0 && live) {
+      int64_t off1, off2;
+      outer_offsets(p, out, off1, off2);
+      *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
+      red_signal(p);
+   }
+}
+
 // ---------------------------------------------------------------------------
 template <class R, class T, int VEC>
-__global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParams p)
+__global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedParams p)
 {
    using A = typename R::acc_t;
    __shared__ A smem[RED_THREADS / 32];
+   __shared__ int shave[RED_THREADS / 32];
+   __shared__ int last_block;
    const uint32_t group = p.group;
    const uint32_t gpb = RED_THREADS / group;
    const uint64_t gid = (uint64_t)blockIdx.x * gpb + threadIdx.x / group;
@@ -148,10 +226,12 @@ __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParam
       const uint64_t nslot = (rowlen + VEC - 1) / VEC;              // vector slots per row (last may be ragged)
       const uint64_t rows = p.relem / rowlen;
       const uint64_t total = rows * nslot;
-      const uint64_t chunk = (total + p.split - 1) / p.split;
-      const uint64_t begin = (uint64_t)s * chunk;
+      constexpr int U = sizeof(T) >= 4 ? 8 : 4;         // vectors in flight per thread (measured: 8 is slower for 1-byte types)
+      // slots per split, rounded up to whole iterations of the dense loop (trailing splits may be empty)
+      uint64_t chunk = (total + p.split - 1) / p.split;
+      chunk = (chunk + (uint64_t)group * U - 1) / ((uint64_t)group * U) * ((uint64_t)group * U);
+      const uint64_t begin = (uint64_t)s * chunk < total ? (uint64_t)s * chunk : total;
       const uint64_t end = begin + chunk < total ? begin + chunk : total;
-      constexpr int U = 4;
       uint64_t slot0 = begin + lane;
       if (rows == 1) {
          // One dense row: whole vectors by pointer increment, nothing predicated per element.
@@ -169,10 +249,11 @@ __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParam
          for (; slot0 < fend; slot0 += group, q += gstep) accum_vec<R, T, VEC>(r, acc, ld_vec<T, VEC>(q));
          // the ragged last slot (fewer than VEC elements) is left to the general loop below
       }
-      for (; slot0 < end; slot0 += (uint64_t)group * U) {
-         Vec<T, VEC> v[U]; int cnt[U];
+      constexpr int UG = 2;                             // general form: index arithmetic per slot, few vectors in flight
+      for (; slot0 < end; slot0 += (uint64_t)group * UG) {
+         Vec<T, VEC> v[UG]; int cnt[UG];
 #pragma unroll
-         for (int u = 0; u < U; u++) {
+         for (int u = 0; u < UG; u++) {
             uint64_t slot = slot0 + (uint64_t)u * group;
             cnt[u] = 0;
             if (slot < end) {
@@ -187,7 +268,7 @@ __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParam
             }
          }
 #pragma unroll
-         for (int u = 0; u < U; u++) {
+         for (int u = 0; u < UG; u++) {
 #pragma unroll
             for (int e = 0; e < VEC; e++) if (e < cnt[u]) r.accum(acc, v[u].v[e]);
          }
@@ -200,21 +281,33 @@ __global__ void __launch_bounds__(RED_THREADS) red_row(const R r, const RedParam
    } else {
       block_fold(r, acc, smem);
       if (threadIdx.x == 0 && live) red_emit(r, p, out, s, off2, acc);
+      if (p.ticket != nullptr) {
+         // One output shared by the `split` blocks of this grid: each block announces its partial on the
+         // stream's counter, and the block that arrives last folds all partials (in index order, so the
+         // result does not depend on which block that is) and leaves the counter at zero for the next launch.
+         if (threadIdx.x == 0) { __threadfence(); last_block = (atomicAdd(p.ticket, 1u) == p.split - 1u); }
+         __syncthreads();
+         if (last_block) {
+            __threadfence();
+            red_fin_body<R, RED_THREADS>(r, p, 0, true, smem, shave);
+            if (threadIdx.x == 0) *p.ticket = 0u;
+         }
+      }
    }
 }
 
 // ---------------------------------------------------------------------------
-// blockDim = (32, 8): x owns VEC adjacent outputs along outer dimension 0, y slices
+// blockDim = (bx, 256 / bx): x owns VEC adjacent outputs along outer dimension 0, y slices
 // the reduced range.
 template <class R, class T, int VEC>
-__global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParams p)
+__global__ void __launch_bounds__(RED_THREADS, RED_MIN_BLOCKS(T)) red_col(const R r, const RedParams p)
 {
    using A = typename R::acc_t;
-   __shared__ A smem[8][32][VEC];
+   __shared__ A smem[RED_THREADS][VEC];                                  // [y * blockDim.x + x]
    uint64_t bid = blockIdx.x;
    const uint32_t s = (uint32_t)(bid % p.split); bid /= p.split;
    const uint64_t tile = bid % p.tiles0; const uint64_t rest = bid / p.tiles0;
-   const uint64_t o0 = (tile * 32 + threadIdx.x) * VEC;                 // first of my outputs along dim 0
+   const uint64_t o0 = (tile * blockDim.x + threadIdx.x) * VEC;         // first of my outputs along dim 0
    const bool live = o0 < (uint64_t)p.size[0];
    const int nmine = live ? (int)(((uint64_t)p.size[0] - o0) < (uint64_t)VEC ? ((uint64_t)p.size[0] - o0) : VEC) : 0;
 
@@ -252,11 +345,27 @@ __global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParam
                for (int e = 0; e < VEC; e++) r.accum(acc[e], v[u].v[e]);
             }
          }
-      }
-      for (; r0 < end; r0 += (uint64_t)blockDim.y * U) {
-         Vec<T, VEC> v[U]; bool ok[U];
+         // the rows left over (fewer than U per y slice) in one more round, all loads issued together
+         if (r0 < end) {
+            Vec<T, VEC> v[U]; bool ok[U];
 #pragma unroll
-         for (int u = 0; u < U; u++) {
+            for (int u = 0; u < U; u++) {
+               ok[u] = r0 + (uint64_t)u * blockDim.y < end;
+               if (ok[u]) v[u] = ld_vec<T, VEC>(q + u * ystep);
+            }
+#pragma unroll
+            for (int u = 0; u < U; u++) if (ok[u]) {
+#pragma unroll
+               for (int e = 0; e < VEC; e++) r.accum(acc[e], v[u].v[e]);
+            }
+            r0 = end;
+         }
+      }
+      constexpr int UG = 2;
+      for (; r0 < end; r0 += (uint64_t)blockDim.y * UG) {
+         Vec<T, VEC> v[UG]; bool ok[UG];
+#pragma unroll
+         for (int u = 0; u < UG; u++) {
             uint64_t rr = r0 + (uint64_t)u * blockDim.y;
             ok[u] = rr < end;
             if (ok[u]) {
@@ -268,19 +377,19 @@ __global__ void __launch_bounds__(RED_THREADS) red_col(const R r, const RedParam
             }
          }
 #pragma unroll
-         for (int u = 0; u < U; u++) if (ok[u]) {
+         for (int u = 0; u < UG; u++) if (ok[u]) {
 #pragma unroll
             for (int e = 0; e < VEC; e++) if (e < nmine) r.accum(acc[e], v[u].v[e]);
          }
       }
    }
 #pragma unroll
-   for (int e = 0; e < VEC; e++) smem[threadIdx.y][threadIdx.x][e] = acc[e];
+   for (int e = 0; e < VEC; e++) smem[threadIdx.y * blockDim.x + threadIdx.x][e] = acc[e];
    __syncthreads();
    if (threadIdx.y == 0 && live) {
       for (int y = 1; y < (int)blockDim.y; y++) {
 #pragma unroll
-         for (int e = 0; e < VEC; e++) r.combine(acc[e], smem[y][threadIdx.x][e]);
+         for (int e = 0; e < VEC; e++) r.combine(acc[e], smem[y * blockDim.x + threadIdx.x][e]);
       }
       const uint64_t outbase = rest * (uint64_t)p.size[0] + o0;
 #pragma unroll
@@ -310,31 +419,14 @@ __global__ void __launch_bounds__(RED_THREADS) red_gen(const R r, const RedParam
 }
 
 // ---------------------------------------------------------------------------
-// One warp per output folds its `split` partials: lane l takes partials l, l+32, ...
-// in order, then the lanes are folded by the shuffle tree.
-template <class R>
+template <class R, int GROUP>
 __global__ void __launch_bounds__(RED_THREADS) red_fin(const R r, const RedParams p)
 {
-   using A = typename R::acc_t; using O = typename R::out_t;
-   const uint64_t out = (uint64_t)blockIdx.x * (RED_THREADS / 32) + (threadIdx.x >> 5);
-   const uint32_t lane = threadIdx.x & 31;
-   const bool live = out < p.nout;
-   const A *part = reinterpret_cast<const A *>(p.buf) + (live ? out : 0) * p.split;
-   A acc = part[lane < p.split ? lane : 0];          // an extra copy of a partial is harmless only for
-   bool have = lane < p.split;                        // idempotent folds, so lanes without one are skipped below
-   for (uint32_t i = lane + 32; i < p.split; i += 32) r.combine(acc, part[i]);
-   // shuffle tree over the lanes that hold data
-#pragma unroll
-   for (int d = 16; d >= 1; d >>= 1) {
-      A other = shfl_down_any<A>(acc, d);
-      bool other_has = __shfl_down_sync(0xFFFFFFFFu, (int)have, d) != 0 && (lane + d < 32);
-      if (have && other_has) r.combine(acc, other);
-   }
-   if (lane == 0 && live) {
-      int64_t off1, off2;
-      outer_offsets(p, out, off1, off2);
-      *reinterpret_cast<O *>(p.dst + off2) = r.finalize(acc);
-   }
+   using A = typename R::acc_t;
+   __shared__ A smem[RED_THREADS / 32];
+   __shared__ int shave[RED_THREADS / 32];
+   const uint64_t out = (uint64_t)blockIdx.x * (RED_THREADS / GROUP) + threadIdx.x / GROUP;
+   red_fin_body<R, GROUP>(r, p, out, out < p.nout, smem, shave);
 }
 
 // ---------------------------------------------------------------------------
@@ -350,7 +442,7 @@ inline uint32_t red_split_cap(uint64_t nout, uint64_t relem, int sms)
 {
    uint64_t by_work = relem / 256; if (by_work < 1) by_work = 1;
    uint64_t tiles = nout / 512; if (tiles < 1) tiles = 1;
-   uint64_t by_fill = ((uint64_t)sms * 8 + tiles - 1) / tiles;
+   uint64_t by_fill = ((uint64_t)sms * RED_WANT_PER_SM + tiles - 1) / tiles;
    uint64_t cap = by_work < by_fill ? by_work : by_fill;
    if (cap < 1) cap = 1;
    if (cap > 65535) cap = 65535;
@@ -387,9 +479,19 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
    DeviceInfo dev;
    if (current_device_info(&dev) != 0) return -1;
    if (!aligned_to(p.src, sizeof(T))) SD_ERROR("Tensor data must be aligned to the element size");
-   const uint64_t want = (uint64_t)dev.sms * 8;
-   auto pick_split = [&](uint64_t units) {
-      uint64_t s = (want + units - 1) / units; if (s < 1) s = 1;
+   // Splitting aims at one resident wave: blocks per multiprocessor that the chosen kernel can hold (asked of
+   // the runtime once per kernel), never more than the RED_WANT_PER_SM that sized the scratch buffer.
+   uint64_t want = (uint64_t)dev.sms * RED_WANT_PER_SM;
+   auto resident = [&](auto kernel, int &cache) {
+      if (cache == 0) {
+         int n = 0;
+         if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, RED_THREADS, 0) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
+         cache = n < 1 ? 1 : (n > RED_WANT_PER_SM ? RED_WANT_PER_SM : n);
+      }
+      want = (uint64_t)dev.sms * cache; };
+   static int occ_row_v = 0, occ_row_s = 0, occ_col_v = 0, occ_col_s = 0;
+   auto pick_split = [&](uint64_t units) {                       // units: blocks the launch has without splitting
+      uint64_t s = (want + units / 2) / units; if (s < 1) s = 1;
       if (s > split_cap) s = split_cap; return (uint32_t)s; };
    if (!p.buf) split_cap = 1;
 
@@ -404,26 +506,34 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
       for (int d = 1; d < p.rdims && vec; d++) if (p.rstride[d] % 16 != 0) vec = false;
       // a warp per output when there are enough outputs to fill the machine with warps (no block
       // barrier, 32 lanes x 4 vectors in flight each), a block per output otherwise
+      if (vec) resident(red_row<R, T, VEC>, occ_row_v); else resident(red_row<R, T, 1>, occ_row_s);
       p.group = (p.relem < 2048 || p.nout >= (uint64_t)dev.sms * 32) ? 32 : 256;
-      p.split = pick_split(p.nout * (p.group / 32) / 8 + 1);
+      p.split = pick_split((p.nout * p.group + RED_THREADS - 1) / RED_THREADS);
       uint64_t groups = p.nout * p.split;
       uint64_t gpb = RED_THREADS / p.group;
       uint64_t blocks = (groups + gpb - 1) / gpb;
       if (blocks > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
+      p.ticket = (p.nout == 1 && p.group == (uint32_t)RED_THREADS && p.split > 1) ? red_ticket_for_stream(stream) : nullptr;
+      fin_needed = p.split > 1 && p.ticket == nullptr;
       if (vec) red_row<R, T, VEC><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
       else     red_row<R, T, 1><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
-      fin_needed = p.split > 1;
    } else if (col_dense) {
       bool vec = VEC > 1 && aligned_to(p.src, 16);
       for (int d = 1; d < p.ndims && vec; d++) if (p.stride1[d] % 16 != 0) vec = false;
       for (int d = 0; d < p.rdims && vec; d++) if (p.rstride[d] % 16 != 0) vec = false;
       const int v = vec ? VEC : 1;
-      p.tiles0 = ((uint64_t)p.size[0] + 32 * v - 1) / (32 * v);
+      if (vec) resident(red_col<R, T, VEC>, occ_col_v); else resident(red_col<R, T, 1>, occ_col_s);
+      // Block shape (bx, 256 / bx): x runs over adjacent outputs, y slices the reduced range.  A wide x makes every
+      // row access of the block one contiguous span (4 KB at bx = 256), which keeps DRAM pages open; narrow output
+      // dimensions get a narrower x so that no thread idles.
+      unsigned bx = 256;
+      while (bx > 32 && (uint64_t)(bx / 2) * v >= (uint64_t)p.size[0]) bx /= 2;
+      p.tiles0 = ((uint64_t)p.size[0] + (uint64_t)bx * v - 1) / ((uint64_t)bx * v);
       uint64_t rest = p.nout / (uint64_t)p.size[0];
       p.split = pick_split(p.tiles0 * rest);
       uint64_t blocks = p.tiles0 * rest * p.split;
       if (blocks > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
-      dim3 bd(32, 8);
+      dim3 bd(bx, RED_THREADS / bx);
       if (vec) red_col<R, T, VEC><<<(unsigned)blocks, bd, 0, stream>>>(r, p);
       else     red_col<R, T, 1><<<(unsigned)blocks, bd, 0, stream>>>(r, p);
       fin_needed = p.split > 1;
@@ -437,8 +547,13 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
    }
    SD_LAUNCH_CHECK();
    if (fin_needed) {
-      uint64_t blocks = (p.nout + (RED_THREADS / 32) - 1) / (RED_THREADS / 32);
-      red_fin<R><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      if (p.split > 64) {
+         if (p.nout > 0x7FFFFFFFull) SD_ERROR("Reduction grid too large");
+         red_fin<R, RED_THREADS><<<(unsigned)p.nout, RED_THREADS, 0, stream>>>(r, p);
+      } else {
+         uint64_t blocks = (p.nout + (RED_THREADS / 32) - 1) / (RED_THREADS / 32);
+         red_fin<R, 32><<<(unsigned)blocks, RED_THREADS, 0, stream>>>(r, p);
+      }
       SD_LAUNCH_CHECK();
    }
    (void)sizeof(A);

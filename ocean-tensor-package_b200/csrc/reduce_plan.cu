@@ -3,6 +3,8 @@
 // Counterparts: solid/src/core/gpu/op/reduce_all.c:77-123 (buffer size),
 // solid/src/core/gpu/op/reduce_axis.c:22-315 (solid_gpu_reduce_axis_prepare).
 #include <cstring>
+#include <mutex>
+#include <unordered_map>
 #include "solid_core_gpu.h"
 #include "reduce.cuh"
 
@@ -10,13 +12,14 @@ namespace sd {
 thread_local void *reduce_all_device_result = nullptr;
 
 // Result slot of the host-returning global reductions: 64 bytes of pinned host memory per
-// device, mapped into the device address space (unified addressing makes the host pointer valid
-// in kernels).  Created the first time a device runs such a reduction and kept until exit.
-// Callers are single-threaded per device (docs/implementation.md of the reference), and each
-// call synchronises before it returns, so one slot per device suffices.
+// (host thread, device), mapped into the device address space (unified addressing makes the
+// host pointer valid in kernels).  Bytes 0-15 receive the value, the word at byte 32 the
+// sequence number of the call once the value is in place; the word at byte 48 is the host's
+// count of calls, from which the sequence numbers are taken.  Created the first time a thread
+// runs such a reduction on a device and kept until exit.
 char *reduce_all_host_slot()
 {
-   static char *slots[64] = {nullptr};
+   static thread_local char *slots[64] = {nullptr};
    int device;
    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) {
       snprintf(solid_errmsg, SOLID_ERRMSG_SIZE, "Error getting the current device");
@@ -29,9 +32,40 @@ char *reduce_all_host_slot()
          snprintf(solid_errmsg, SOLID_ERRMSG_SIZE, "Error allocating the pinned result slot (%s)", cudaGetErrorString(st));
          return nullptr;
       }
+      memset(p, 0, 64);
       slots[device] = (char *)p;
    }
    return slots[device];
+}
+
+// Arrival counters of the single-pass folds: one word per stream of a device, in a device array
+// that the module loader zeroes; the last block of every launch writes its word back to zero.
+// Launches of one stream run one after another, so they can share a word; two streams never do.
+constexpr int RED_TICKETS = 1024;
+__device__ unsigned int red_ticket_pool[RED_TICKETS];
+
+unsigned int *red_ticket_for_stream(cudaStream_t stream)
+{
+   struct PerDevice { unsigned int *base = nullptr; std::unordered_map<cudaStream_t, int> index; };
+   static PerDevice table[64];
+   static std::mutex lock;
+   if (stream == cudaStreamPerThread) return nullptr;       // one handle, a different stream in every host thread
+   if (stream == cudaStreamLegacy) stream = nullptr;        // both name the legacy default stream
+   int device;
+   if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return nullptr;
+   std::lock_guard<std::mutex> guard(lock);
+   PerDevice &t = table[device];
+   if (t.base == nullptr) {
+      void *p = nullptr;
+      if (cudaGetSymbolAddress(&p, red_ticket_pool) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
+      t.base = (unsigned int *)p;
+   }
+   auto it = t.index.find(stream);
+   if (it != t.index.end()) return t.base + it->second;
+   if ((int)t.index.size() >= RED_TICKETS) return nullptr;
+   const int idx = (int)t.index.size();
+   t.index.emplace(stream, idx);
+   return t.base + idx;
 }
 } // namespace sd
 

@@ -263,3 +263,34 @@ def test_axis_norm_p(gpu, cpu):
             with np.errstate(invalid="ignore"):
                 ok = (np.isnan(g) & np.isnan(w)) | (g == w) | (np.abs(g - w) <= 2e-3 * np.abs(w) + 1e-30)
             assert ok.all(), "axis_norm_%s axes %s" % (dtype, axes)
+
+
+@pytest.mark.gpu
+def test_global_reductions_on_several_streams(gpu, cpu):
+    """Split global reductions fold their partials in the last block to arrive, which is found through a
+    counter kept per stream: interleave host-returning and device-resident calls on four streams
+    (the default one included) and repeat them, so that every counter is used again after it was reset."""
+    import torch
+    dev = util.Device()
+    rng = np.random.default_rng(77)
+    n = (1 << 20) + 17
+    hosts = [rng.integers(-1000, 1000, n).astype(np.int32) for _ in range(4)]
+    want = [decode(cpu.reduce_all("sum", "int32", [n], [4], h.ctypes.data), "int64") for h in hosts]
+    wmax = [decode(cpu.reduce_all("maximum", "int32", [n], [4], h.ctypes.data), "int32") for h in hosts]
+    data = [dev.upload(h.view(np.uint8)) for h in hosts]
+    streams = [torch.cuda.current_stream()] + [torch.cuda.Stream() for _ in range(3)]
+    scratch = [dev.empty(gpu.reduce_all_buffer_size(n, 0) + 64) for _ in range(4)]
+    results = [dev.empty(16) for _ in range(4)]
+    torch.cuda.synchronize()
+    for _ in range(5):
+        for k in range(4):      # device-resident: nothing waits, the four streams overlap
+            gpu.reduce_all_device("sum", "int32", [n], [4], data[k].data_ptr(), results[k].data_ptr(),
+                                  scratch[k].data_ptr(), streams[k].cuda_stream)
+        for k in range(4):      # host-returning on the same streams, queued behind the calls above
+            got = decode(gpu.reduce_all("maximum", "int32", [n], [4], data[k].data_ptr(), scratch[k].data_ptr(),
+                                        streams[k].cuda_stream), "int32")
+            assert got == wmax[k], ("maximum", k)
+        torch.cuda.synchronize()
+        for k in range(4):
+            got = dev.download(results[k])[:8].view(np.int64)[0]
+            assert got == want[k][0], ("sum", k)
