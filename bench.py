@@ -234,7 +234,7 @@ def time_call(fn, iters: int):
     return (t1 - t0) / iters
 
 
-def ops_table(peak: float, with_cpu: bool):
+def ops_table(peak: float, with_cpu: bool, only=None, iters_scale: float = 1.0):
     """One row per named operation of configurations 1-4: GB/s on algorithmic bytes."""
     import torch
     from solid_b200 import Tensor, ops, _lib, dtypes as dt
@@ -248,7 +248,8 @@ def ops_table(peak: float, with_cpu: bool):
             cpu = ref.get(); cpu.set_threads(os.cpu_count() or 1)
 
     def add_row(config, name, nbytes, fn, cpu_fn=None, iters=20, queued=True):
-        t = time_gpu(fn, iters, queued=queued)
+        iters = max(1, int(iters * iters_scale))
+        t = time_gpu(fn, iters, warmup=3 if iters_scale >= 1 else 1, queued=queued)
         row = {"config": config, "op": name, "bytes": nbytes, "us": t * 1e6, "gbs": nbytes / t / 1e9,
                "frac_measured": nbytes / t / 1e9 / peak, "frac_8tbs": nbytes / t / 1e9 / NOMINAL_HBM_GBS,
                "issue_us": time_call(fn, iters) * 1e6}
@@ -260,108 +261,113 @@ def ops_table(peak: float, with_cpu: bool):
     def dev(arr, dtype=None):
         return Tensor.from_numpy(arr, dtype)
 
-    # ---- C1: float32 1-D, n = 2^24; three distinct buffer sets so 67-200 MB working sets are not L2 hits
-    n = 1 << 24
-    hx = [rng.uniform(-1, 1, n).astype(np.float32) for _ in range(3)]
-    hy = [rng.uniform(-1, 1, n).astype(np.float32) for _ in range(3)]
-    xs, ys = [dev(a) for a in hx], [dev(a) for a in hy]
-    zs = [Tensor.empty([n], "float") for _ in range(3)]
-    state = {"i": 0}
-
-    def rot():
-        state["i"] = (state["i"] + 1) % 3
-        return state["i"]
-    hz = np.empty(n, dtype=np.float32)
-    for name in ("add", "multiply"):
-        add_row("C1", name + " f32 2^24", 12 * n,
-                lambda name=name: (lambda i: ops.binary(name, xs[i], ys[i], zs[i]))(rot()),
-                (lambda name=name: cpu.binary(name, "float", [n], [4], hx[0].ctypes.data, [4], hy[0].ctypes.data, [4], hz.ctypes.data)) if cpu else None)
-    for name in ("sum", "norm2", "maximum"):
-        add_row("C1", name + " f32 2^24 (incl. host read-back)", 4 * n,
-                lambda name=name: ops.reduce_all(name, xs[rot()]),
-                (lambda name=name: cpu.reduce_all(name, "float", [n], [4], hx[0].ctypes.data)) if cpu else None, queued=False)
     rbuf = torch.empty(lib.reduce_all_buffer_size(1 << 26, 0), dtype=torch.uint8, device="cuda")
     rres = torch.empty(16, dtype=torch.uint8, device="cuda")
     cur = torch.cuda.current_stream().cuda_stream
-    for name in ("sum", "norm2", "maximum"):
-        add_row("C1", name + " f32 2^24 (result stays on the device)", 4 * n,
-                lambda name=name: (lambda i: lib.reduce_all_device(name, "float", [n], [4], xs[i].ptr, rres.data_ptr(),
-                                                                   rbuf.data_ptr(), cur))(rot()))
+
+    # ---- C1: float32 1-D, n = 2^24; three distinct buffer sets so 67-200 MB working sets are not L2 hits
+    if only in (None, "C1"):
+        n = 1 << 24
+        hx = [rng.uniform(-1, 1, n).astype(np.float32) for _ in range(3)]
+        hy = [rng.uniform(-1, 1, n).astype(np.float32) for _ in range(3)]
+        xs, ys = [dev(a) for a in hx], [dev(a) for a in hy]
+        zs = [Tensor.empty([n], "float") for _ in range(3)]
+        state = {"i": 0}
+
+        def rot():
+            state["i"] = (state["i"] + 1) % 3
+            return state["i"]
+        hz = np.empty(n, dtype=np.float32)
+        for name in ("add", "multiply"):
+            add_row("C1", name + " f32 2^24", 12 * n,
+                    lambda name=name: (lambda i: ops.binary(name, xs[i], ys[i], zs[i]))(rot()),
+                    (lambda name=name: cpu.binary(name, "float", [n], [4], hx[0].ctypes.data, [4], hy[0].ctypes.data, [4], hz.ctypes.data)) if cpu else None)
+        for name in ("sum", "norm2", "maximum"):
+            add_row("C1", name + " f32 2^24 (incl. host read-back)", 4 * n,
+                    lambda name=name: ops.reduce_all(name, xs[rot()]),
+                    (lambda name=name: cpu.reduce_all(name, "float", [n], [4], hx[0].ctypes.data)) if cpu else None, queued=False)
+        for name in ("sum", "norm2", "maximum"):
+            add_row("C1", name + " f32 2^24 (result stays on the device)", 4 * n,
+                    lambda name=name: (lambda i: lib.reduce_all_device(name, "float", [n], [4], xs[i].ptr, rres.data_ptr(),
+                                                                       rbuf.data_ptr(), cur))(rot()))
 
     # ---- C2: C(f32) = A(f64, transposed) * B(i32, byteswapped) + r(f32 row broadcast), 4096^2; unaligned byteswapped f64 -> f16
-    m = 4096
-    A = rng.uniform(-1, 1, (m, m))                                   # row-major buffer viewed transposed
-    B = rng.integers(-1000, 1001, (m, m)).astype(np.int32)
-    r = rng.uniform(-1, 1, m).astype(np.float32)
-    tA = Tensor(torch.from_numpy(A.view(np.uint8).reshape(-1)).cuda(), "double", [m, m], [8 * m, 8])
-    tB = Tensor(torch.from_numpy(B.astype(">i4").view(np.uint8).reshape(-1)).cuda(), "int32", [m, m], [4, 4 * m], byteswapped=True)
-    tr = Tensor(torch.from_numpy(r.view(np.uint8)).cuda(), "float", [m, m], [0, 4])
-    tC = Tensor.empty([m, m], "float")
-    add_row("C2", "fused C=f32(A_f64^T * bswap(B_i32) + r_f32) 4096^2", 16 * m * m,
-            lambda: ops.multiply_add(tA, tB, tr, tC))
-    raw = np.zeros(8 * m * m + 64, dtype=np.uint8)
-    raw[3: 3 + 8 * m * m] = A.astype(">f8").view(np.uint8).reshape(-1)
-    tU = Tensor(torch.from_numpy(raw).cuda(), "double", [m * m], [8], offset=3, byteswapped=True)
-    tH = Tensor.empty([m * m], "half")
-    hH = np.empty(m * m, dtype=np.uint16)
-    add_row("C2", "copy f64 (offset 3 B, byteswapped) -> f16 4096^2", 10 * m * m, lambda: ops.copy(tU, tH),
-            (lambda: cpu.copy("double", "half", [m * m], [8], raw.ctypes.data + 3, [m * m], [2], hH.ctypes.data, variant="byteswap_copy")) if cpu else None)
-    del tA, tB, tC, tU, tH
+    if only in (None, "C2"):
+        m = 4096
+        A = rng.uniform(-1, 1, (m, m))                                   # row-major buffer viewed transposed
+        B = rng.integers(-1000, 1001, (m, m)).astype(np.int32)
+        r = rng.uniform(-1, 1, m).astype(np.float32)
+        tA = Tensor(torch.from_numpy(A.view(np.uint8).reshape(-1)).cuda(), "double", [m, m], [8 * m, 8])
+        tB = Tensor(torch.from_numpy(B.astype(">i4").view(np.uint8).reshape(-1)).cuda(), "int32", [m, m], [4, 4 * m], byteswapped=True)
+        tr = Tensor(torch.from_numpy(r.view(np.uint8)).cuda(), "float", [m, m], [0, 4])
+        tC = Tensor.empty([m, m], "float")
+        add_row("C2", "fused C=f32(A_f64^T * bswap(B_i32) + r_f32) 4096^2", 16 * m * m,
+                lambda: ops.multiply_add(tA, tB, tr, tC))
+        raw = np.zeros(8 * m * m + 64, dtype=np.uint8)
+        raw[3: 3 + 8 * m * m] = A.astype(">f8").view(np.uint8).reshape(-1)
+        tU = Tensor(torch.from_numpy(raw).cuda(), "double", [m * m], [8], offset=3, byteswapped=True)
+        tH = Tensor.empty([m * m], "half")
+        hH = np.empty(m * m, dtype=np.uint16)
+        add_row("C2", "copy f64 (offset 3 B, byteswapped) -> f16 4096^2", 10 * m * m, lambda: ops.copy(tU, tH),
+                (lambda: cpu.copy("double", "half", [m * m], [8], raw.ctypes.data + 3, [m * m], [2], hH.ctypes.data, variant="byteswap_copy")) if cpu else None)
+        del tA, tB, tC, tU, tH
 
     # ---- C3: axis reductions on 8192^2 (column-major: axis 0 is the dense one), global any/all/nnz on bool
-    k = 8192
-    for dtype, npdt, gen in (("float", np.float32, lambda: rng.normal(size=(k, k)).astype(np.float32)),
-                             ("int64", np.int64, lambda: rng.integers(-2 ** 20, 2 ** 20, (k, k), dtype=np.int64))):
-        h = np.asfortranarray(gen())
-        t = dev(h)
-        es = dt.SIZE[dtype]
-        for name in ("sum", "minimum", "maximum", "norm2"):
-            for axis in (0, 1):
-                rtype = {"sum": dtype, "minimum": dtype, "maximum": dtype, "norm2": "float" if dtype == "float" else "double"}[name]
-                out = Tensor.empty([k], rtype)
-                hout = np.empty(k, dtype=dt.NUMPY[rtype])
-                keep = 1 - axis
-                add_row("C3", "axis_%s %s 8192^2 axis %d" % (name, dtype, axis), es * k * k,
-                        lambda name=name, axis=axis, out=out: ops.reduce_axis(name, t, axis, out), iters=10,
-                        cpu_fn=(lambda name=name, axis=axis, keep=keep, hout=hout: cpu.reduce_axis(
-                            "axis_" + name, dtype, [k], [h.strides[keep]], h.ctypes.data, [hout.itemsize], hout.ctypes.data,
-                            [k], [h.strides[axis]])) if cpu else None)
-        del t, h
-    hb = (rng.random((k, k)) < 0.1).astype(np.uint8)
-    tb = dev(hb, "bool")
-    for name in ("any", "all", "nnz"):
-        add_row("C3", "%s bool 8192^2 (incl. host read-back)" % name, k * k, lambda name=name: ops.reduce_all(name, tb),
-                (lambda name=name: cpu.reduce_all(name, "bool", [k * k], [1], hb.ctypes.data)) if cpu else None, queued=False)
-        add_row("C3", "%s bool 8192^2 (result stays on the device)" % name, k * k,
-                lambda name=name: lib.reduce_all_device(name, "bool", [k * k], [1], tb.ptr, rres.data_ptr(), rbuf.data_ptr(), cur))
-    del tb
+    if only in (None, "C3"):
+        k = 8192
+        for dtype, npdt, gen in (("float", np.float32, lambda: rng.normal(size=(k, k)).astype(np.float32)),
+                                 ("int64", np.int64, lambda: rng.integers(-2 ** 20, 2 ** 20, (k, k), dtype=np.int64))):
+            h = np.asfortranarray(gen())
+            t = dev(h)
+            es = dt.SIZE[dtype]
+            for name in ("sum", "minimum", "maximum", "norm2"):
+                for axis in (0, 1):
+                    rtype = {"sum": dtype, "minimum": dtype, "maximum": dtype, "norm2": "float" if dtype == "float" else "double"}[name]
+                    out = Tensor.empty([k], rtype)
+                    hout = np.empty(k, dtype=dt.NUMPY[rtype])
+                    keep = 1 - axis
+                    add_row("C3", "axis_%s %s 8192^2 axis %d" % (name, dtype, axis), es * k * k,
+                            lambda name=name, axis=axis, out=out: ops.reduce_axis(name, t, axis, out), iters=10,
+                            cpu_fn=(lambda name=name, axis=axis, keep=keep, hout=hout: cpu.reduce_axis(
+                                "axis_" + name, dtype, [k], [h.strides[keep]], h.ctypes.data, [hout.itemsize], hout.ctypes.data,
+                                [k], [h.strides[axis]])) if cpu else None)
+            del t, h
+        hb = (rng.random((k, k)) < 0.1).astype(np.uint8)
+        tb = dev(hb, "bool")
+        for name in ("any", "all", "nnz"):
+            add_row("C3", "%s bool 8192^2 (incl. host read-back)" % name, k * k, lambda name=name: ops.reduce_all(name, tb),
+                    (lambda name=name: cpu.reduce_all(name, "bool", [k * k], [1], hb.ctypes.data)) if cpu else None, queued=False)
+            add_row("C3", "%s bool 8192^2 (result stays on the device)" % name, k * k,
+                    lambda name=name: lib.reduce_all_device(name, "bool", [k * k], [1], tb.ptr, rres.data_ptr(), rbuf.data_ptr(), cur))
+        del tb
 
     # ---- C4: unary chain on 2^26 elements
-    n4 = 1 << 26
-    hf = rng.uniform(0.01, 10, n4).astype(np.float32)
-    tf, to = dev(hf), Tensor.empty([n4], "float")
-    ho = np.empty(n4, dtype=np.float32)
-    for name in ("sqrt", "exp", "log", "sin", "fabs"):
-        add_row("C4", "%s f32 2^26" % name, 8 * n4, lambda name=name: ops.unary(name, tf, to), iters=10,
-                cpu_fn=(lambda name=name: cpu.unary(name, "float", [n4], [4], hf.ctypes.data, [4], ho.ctypes.data)) if cpu else None)
-    del tf, to
-    hc = (rng.normal(size=n4) + 1j * rng.normal(size=n4)).astype(np.complex128)
-    hd = (rng.normal(size=n4) + 1j * rng.normal(size=n4)).astype(np.complex128)
-    tc, td, tz = dev(hc), dev(hd), Tensor.empty([n4], "cdouble")
-    ta = Tensor.empty([n4], "double")
-    hz2 = np.empty(n4, dtype=np.complex128)
-    add_row("C4", "conj c128 2^26", 32 * n4, lambda: ops.unary("conj", tc, tz), iters=5,
-            cpu_fn=(lambda: cpu.unary("conj", "cdouble", [n4], [16], hc.ctypes.data, [16], hz2.ctypes.data)) if cpu else None)
-    add_row("C4", "absolute c128 2^26", 24 * n4, lambda: ops.unary("absolute", tc, ta), iters=5,
-            cpu_fn=(lambda: cpu.unary("absolute", "cdouble", [n4], [16], hc.ctypes.data, [8], hz2.ctypes.data)) if cpu else None)
-    add_row("C4", "multiply c128 2^26", 48 * n4, lambda: ops.binary("multiply", tc, td, tz), iters=5,
-            cpu_fn=(lambda: cpu.binary("multiply", "cdouble", [n4], [16], hc.ctypes.data, [16], hd.ctypes.data, [16], hz2.ctypes.data)) if cpu else None)
-    del tc, td, tz, ta, hc, hd, hz2
-    from oracle import solid_numpy as sn
-    hh = sn.float_to_half(rng.uniform(-4, 4, n4).astype(np.float32))
-    hg = sn.float_to_half(rng.uniform(-4, 4, n4).astype(np.float32))
-    th, tg, tq = dev(hh, "half"), dev(hg, "half"), Tensor.empty([n4], "half")
-    add_row("C4", "fused a*x+y f16 2^26", 6 * n4, lambda: ops.axpy(0.5, th, tg, tq), iters=10)
+    if only in (None, "C4"):
+        n4 = 1 << 26
+        hf = rng.uniform(0.01, 10, n4).astype(np.float32)
+        tf, to = dev(hf), Tensor.empty([n4], "float")
+        ho = np.empty(n4, dtype=np.float32)
+        for name in ("sqrt", "exp", "log", "sin", "fabs"):
+            add_row("C4", "%s f32 2^26" % name, 8 * n4, lambda name=name: ops.unary(name, tf, to), iters=10,
+                    cpu_fn=(lambda name=name: cpu.unary(name, "float", [n4], [4], hf.ctypes.data, [4], ho.ctypes.data)) if cpu else None)
+        del tf, to
+        hc = (rng.normal(size=n4) + 1j * rng.normal(size=n4)).astype(np.complex128)
+        hd = (rng.normal(size=n4) + 1j * rng.normal(size=n4)).astype(np.complex128)
+        tc, td, tz = dev(hc), dev(hd), Tensor.empty([n4], "cdouble")
+        ta = Tensor.empty([n4], "double")
+        hz2 = np.empty(n4, dtype=np.complex128)
+        add_row("C4", "conj c128 2^26", 32 * n4, lambda: ops.unary("conj", tc, tz), iters=5,
+                cpu_fn=(lambda: cpu.unary("conj", "cdouble", [n4], [16], hc.ctypes.data, [16], hz2.ctypes.data)) if cpu else None)
+        add_row("C4", "absolute c128 2^26", 24 * n4, lambda: ops.unary("absolute", tc, ta), iters=5,
+                cpu_fn=(lambda: cpu.unary("absolute", "cdouble", [n4], [16], hc.ctypes.data, [8], hz2.ctypes.data)) if cpu else None)
+        add_row("C4", "multiply c128 2^26", 48 * n4, lambda: ops.binary("multiply", tc, td, tz), iters=5,
+                cpu_fn=(lambda: cpu.binary("multiply", "cdouble", [n4], [16], hc.ctypes.data, [16], hd.ctypes.data, [16], hz2.ctypes.data)) if cpu else None)
+        del tc, td, tz, ta, hc, hd, hz2
+        from oracle import solid_numpy as sn
+        hh = sn.float_to_half(rng.uniform(-4, 4, n4).astype(np.float32))
+        hg = sn.float_to_half(rng.uniform(-4, 4, n4).astype(np.float32))
+        th, tg, tq = dev(hh, "half"), dev(hg, "half"), Tensor.empty([n4], "half")
+        add_row("C4", "fused a*x+y f16 2^26", 6 * n4, lambda: ops.axpy(0.5, th, tg, tq), iters=10)
     torch.cuda.synchronize()
     return rows
 
@@ -556,10 +562,18 @@ def main():
     ap.add_argument("--log2n", type=int, default=32, help="log2 of the total element count (32 = the named workload)")
     ap.add_argument("--no-ops", action="store_true", help="skip the per-operation table of configurations 1-4")
     ap.add_argument("--no-cpu", action="store_true", help="skip the Solid CPU baselines")
+    ap.add_argument("--ops-only", default=None, choices=["C1", "C2", "C3", "C4"],
+                    help="run only the per-operation rows of one configuration, a few calls each, and print them "
+                         "(a small case for profilers; no headline measurement)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
-    if args.impl == "reference":
+    if args.ops_only:
+        import torch
+        torch.cuda.set_device(0)
+        peak, _ = measured_peak()
+        print(json.dumps({"ops": ops_table(peak, with_cpu=False, only=args.ops_only, iters_scale=0.1)}))
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

@@ -17,30 +17,76 @@ SOLID_GPU_BINARY_OPS(SD_DEFINE_BINARY)
 namespace sd {
 template <class T> struct AxpyApply {
    static constexpr int NIN = 2;
+   static constexpr bool VECTOR = is_half<T>;
+   static constexpr int MIN_BLOCKS = is_half<T> ? 4 : 0;
    using in1_t = T; using in2_t = T; using out_t = T;
    T a;
    SD_D T operator()(T x, T y) const
    {
       using W = work_t<T>;
+      T prod = from_work<T>(to_work<T>(a) * to_work<T>(x));
+      return from_work<T>((W)(to_work<T>(prod) + to_work<T>(y)));
+   }
+   // Half, a whole vector at a time.  While the product and the sum of every element stay inside the normal half
+   // range, the two roundings of the reference (half.c rounds half away from zero) are done on the float bits:
+   // "add half a unit of the 13 dropped bits, clear them".  The inputs then need the hardware conversion only
+   // (its one difference from half.c, -0 for +0, cannot survive a non-zero product or sum), and the result is
+   // exactly representable, so the hardware conversion back is exact.  One out-of-range element (zero, subnormal,
+   // overflow, inf, nan) sends the whole vector through the per-element form above, out of line.
+   template <int N> SD_D Vec<T, N> vec(const Vec<T, N> &x, const Vec<T, N> &y) const
+   {
       if constexpr (is_half<T>) {
-         // Same values as the generic form below with fewer instructions.  (1) The inputs are
-         // decoded by the hardware conversion alone: its only difference from half.c, -0 instead
-         // of +0, cannot reach the result, because a zero product is re-encoded as +0 before the
-         // addition and a zero sum is encoded as +0 at the end.  (2) Rounding the product to half
-         // and decoding it again is done on the float bits: for the normal half range that is
-         // "add half a unit of the 13 dropped bits, clear them".
-         const float xf = __half2float(__ushort_as_half(x.v)), yf = __half2float(__ushort_as_half(y.v));
          const float af = __half2float(__ushort_as_half(a.v));
-         const float p = af * xf;
-         const uint32_t raw = __float_as_uint(p);
-         float pr;
-         if (((raw >> 23) & 0xFFu) - 113u < 29u) pr = __uint_as_float((raw + 0x1000u) & 0xFFFFE000u);
-         else pr = half_to_float(float_to_half(p));
-         return float_to_half(pr + yf);
+         float w[N];
+         // magnitude bits of every product and of every sum: smallest and largest over the vector
+         uint32_t plo = 0x7FFFFFFFu, phi = 0u, slo = 0x7FFFFFFFu, shi = 0u;
+#pragma unroll
+         for (int j = 0; j < N; j += 2) {
+            float s[2]; uint32_t pm[2], sm[2];
+#pragma unroll
+            for (int e = 0; e < 2 && j + e < N; e++) {
+               const float xf = __half2float(__ushort_as_half(x.v[j + e].v)), yf = __half2float(__ushort_as_half(y.v[j + e].v));
+               const uint32_t praw = __float_as_uint(af * xf);
+               pm[e] = praw & 0x7FFFFFFFu;
+               s[e] = __uint_as_float((praw + 0x1000u) & 0xFFFFE000u) + yf;
+               const uint32_t sraw = __float_as_uint(s[e]);
+               sm[e] = sraw & 0x7FFFFFFFu;
+               w[j + e] = __uint_as_float((sraw + 0x1000u) & 0xFFFFE000u);
+            }
+            if (j + 1 < N) {
+               plo = __vimin3_u32(plo, pm[0], pm[1]); phi = __vimax3_u32(phi, pm[0], pm[1]);
+               slo = __vimin3_u32(slo, sm[0], sm[1]); shi = __vimax3_u32(shi, sm[0], sm[1]);
+            } else {
+               plo = min(plo, pm[0]); phi = max(phi, pm[0]); slo = min(slo, sm[0]); shi = max(shi, sm[0]);
+            }
+         }
+         // 2^-14 <= |product| < 2^15 and 2^-14 <= |sum| < 2^16 (nan and inf have the largest magnitude bits)
+         const bool plain = plo >= 0x38800000u && phi < 0x47000000u && slo >= 0x38800000u && shi < 0x47800000u;
+         Vec<T, N> o;
+         if (plain) {
+#pragma unroll
+            for (int j = 0; j + 1 < N; j += 2) {
+               const __half2 h = __floats2half2_rn(w[j], w[j + 1]);
+               o.v[j].v = __half_as_ushort(__low2half(h)); o.v[j + 1].v = __half_as_ushort(__high2half(h));
+            }
+            if (N & 1) o.v[N - 1].v = __half_as_ushort(__float2half_rn(w[N - 1]));
+         } else {
+            o = rare<N>(x, y);
+         }
+         return o;
       } else {
-         T prod = from_work<T>(to_work<T>(a) * to_work<T>(x));
-         return from_work<T>((W)(to_work<T>(prod) + to_work<T>(y)));
+         Vec<T, N> o;
+#pragma unroll
+         for (int j = 0; j < N; j++) o.v[j] = (*this)(x.v[j], y.v[j]);
+         return o;
       }
+   }
+   template <int N> __device__ __noinline__ Vec<T, N> rare(Vec<T, N> x, Vec<T, N> y) const      // by value: stays in registers
+   {
+      Vec<T, N> o;
+#pragma unroll
+      for (int j = 0; j < N; j++) o.v[j] = (*this)(x.v[j], y.v[j]);
+      return o;
    }
 };
 } // namespace sd

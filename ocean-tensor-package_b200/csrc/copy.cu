@@ -43,10 +43,10 @@ __global__ void __launch_bounds__(EW_THREADS) ew_reshape(const A apply, const Re
         idx += (uint64_t)gridDim.x * EW_THREADS) {
       int64_t o1 = 0, o2 = 0;
       uint64_t r = idx;
-      for (int d = 0; d < p.nd1 - 1; d++) { uint64_t q = r / (uint64_t)p.size1[d]; o1 += (int64_t)(r - q * p.size1[d]) * p.stride1[d]; r = q; }
+      for (int d = 0; d < p.nd1 - 1; d++) { uint64_t q = udiv64(r, (uint64_t)p.size1[d]); o1 += (int64_t)(r - q * p.size1[d]) * p.stride1[d]; r = q; }
       o1 += (int64_t)r * p.stride1[p.nd1 - 1];
       r = idx;
-      for (int d = 0; d < p.nd2 - 1; d++) { uint64_t q = r / (uint64_t)p.size2[d]; o2 += (int64_t)(r - q * p.size2[d]) * p.stride2[d]; r = q; }
+      for (int d = 0; d < p.nd2 - 1; d++) { uint64_t q = udiv64(r, (uint64_t)p.size2[d]); o2 += (int64_t)(r - q * p.size2[d]) * p.stride2[d]; r = q; }
       o2 += (int64_t)r * p.stride2[p.nd2 - 1];
       Vec<S, 1> a = ew_load<S, 1, UNAL>(p.src + o1, false, p.unal & 1u);
       Vec<D, 1> o; o.v[0] = apply(a.v[0], Nothing());

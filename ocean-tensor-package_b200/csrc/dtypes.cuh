@@ -18,6 +18,14 @@ namespace sd {
 #define SD_HD __host__ __device__ __forceinline__
 #define SD_D  __device__ __forceinline__
 
+// 64-bit unsigned division is a long emulated sequence on the GPU; nearly every quotient the
+// kernels need has both operands below 2^32, where a single 32-bit division does.
+SD_D uint64_t udiv64(uint64_t a, uint64_t b)
+{
+   if (((a | b) >> 32) == 0) return (uint32_t)a / (uint32_t)b;
+   return a / b;
+}
+
 // Distinct C++ types for the fifteen table indices.  bool and half share a
 // representation with uint8/uint16 but not their semantics, so they are wrapped.
 struct Bool { uint8_t v; };
@@ -79,9 +87,8 @@ SD_HD float half_to_float(Half hh)
    // the hardware conversion is exact for zero, subnormal and normal inputs; only the
    // two deviations of half.c are patched in: +-0 -> +0, and inf/nan rebuilt from the bits
    const uint32_t h = hh.v;
-   float f = __half2float(__ushort_as_half(hh.v));
+   float f = __half2float(__ushort_as_half(hh.v)) + 0.0f;              // -0 + +0 = +0, every other value unchanged
    if ((h & 0x7C00u) == 0x7C00u) f = __uint_as_float(((h & 0x8000u) << 16) | 0x7F800000u | ((h & 0x03FFu) << 13));
-   if ((h & 0x7FFFu) == 0) f = 0.0f;
    return f;
 #else
    uint32_t h = hh.v;
@@ -109,36 +116,44 @@ SD_HD float half_to_float(Half hh)
 // latter running into the inf/nan patterns); the 13 dropped mantissa bits round
 // half AWAY from zero (>= 0x1000 adds one); exponent >= 144 gives +-inf; NaN
 // gives 0x7F00.
+// general form, branch free: the regular encoding (16-bit wrap-around included), then the overrides
+SD_HD uint32_t float_to_half_bits(uint32_t raw)
+{
+   const uint32_t d = raw & 0x007FFFFFu;
+   const uint32_t e = (raw >> 23) & 0xFFu;
+   const uint32_t s = (raw >> 16) & 0x8000u;
+   uint32_t x = ((((e - 112u) << 10) | (d >> 13) | s) + ((d & 0x1FFFu) >= 0x1000u ? 1u : 0u)) & 0xFFFFu;
+   const uint32_t special = (e == 255u && d != 0) ? 0x7F00u : (s | 0x7C00u);
+   x = (e > 143u) ? special : x;
+   x = (e < 112u) ? 0u : x;
+   return x;
+}
+#ifdef __CUDACC__
+// Out of line on the device: values outside the normal half range are rare, and keeping this code out of the
+// unrolled element loops keeps those loops inside the instruction cache.
+__device__ __noinline__ inline uint32_t float_to_half_bits_rare(uint32_t raw) { return float_to_half_bits(raw); }
+#endif
+
 SD_HD Half float_to_half(float f)
 {
    uint32_t raw;
 #ifdef __CUDA_ARCH__
    raw = __float_as_uint(f);
+   // Normal half range (biased float exponent 113..142): half.c rounds the 13 dropped mantissa bits half away
+   // from zero, which on the float bits is "add half a unit, clear the bits"; the value is then exactly
+   // representable and the hardware conversion only re-biases it.  A carry out of the mantissa into the
+   // exponent behaves the same in both encodings.
+   const uint32_t e = (raw >> 23) & 0xFFu;
+   Half r;
+   if (e - 113u < 30u)        r.v = __half_as_ushort(__float2half_rn(__uint_as_float((raw + 0x1000u) & 0xFFFFE000u)));
+   else if ((raw << 1) == 0u) r.v = 0;                                // +-0 -> +0 (zeros are common, keep them inline)
+   else                       r.v = (uint16_t)float_to_half_bits_rare(raw);
+   return r;
 #else
    __builtin_memcpy(&raw, &f, 4);
-#endif
-   const uint32_t d = raw & 0x007FFFFFu;
-   const uint32_t e = (raw >> 23) & 0xFFu;
-   const uint32_t s = (raw >> 16) & 0x8000u;
-#ifdef __CUDA_ARCH__
-   // Normal half range (biased float exponent 113..142): the result is the hardware
-   // round-to-nearest-even conversion, except on an exact tie that RNE rounded down (kept
-   // mantissa bit 13 clear), where half.c rounds away from zero.  A carry out of the mantissa
-   // into the exponent behaves the same in both encodings.
-   if (e - 113u < 30u) {
-      uint32_t x = __half_as_ushort(__float2half_rn(f));
-      x += ((raw & 0x3FFFu) == 0x1000u) ? 1u : 0u;
-      Half r; r.v = (uint16_t)x;
-      return r;
-   }
-#endif
-   // general form, branch free: the regular encoding (16-bit wrap-around included), then the overrides
-   uint32_t x = ((((e - 112u) << 10) | (d >> 13) | s) + ((d & 0x1FFFu) >= 0x1000u ? 1u : 0u)) & 0xFFFFu;
-   const uint32_t special = (e == 255u && d != 0) ? 0x7F00u : (s | 0x7C00u);
-   x = (e > 143u) ? special : x;
-   x = (e < 112u) ? 0u : x;
-   Half r; r.v = (uint16_t)x;
+   Half r; r.v = (uint16_t)float_to_half_bits(raw);
    return r;
+#endif
 }
 
 // ---------------------------------------------------------------------------

@@ -63,6 +63,28 @@ template <class A> struct ew_traits {
    static constexpr int UNROLL = (64 / (VEC * s_max)) > 0 ? (64 / (VEC * s_max)) : 1;
 };
 
+// An apply object may provide   template <int N> Vec<out_t, N> vec(const Vec<in1_t, N> &, const Vec<in2_t, N> &) const
+// next to its per-element operator() (announced by  static constexpr bool VECTOR = true): it then sees the
+// whole vector of a thread-iteration and can take shortcuts that depend on all of its elements.
+// An apply object may also ask for a number of resident blocks per multiprocessor (static constexpr int MIN_BLOCKS).
+template <class A, class = void> struct ew_min_blocks { static constexpr int value = 1; };
+template <class A> struct ew_min_blocks<A, std::enable_if_t<(A::MIN_BLOCKS > 0)>> { static constexpr int value = A::MIN_BLOCKS; };
+template <class A, class = void> struct has_vector_apply : std::false_type {};
+template <class A> struct has_vector_apply<A, std::enable_if_t<A::VECTOR>> : std::true_type {};
+
+template <class A, int N>
+SD_D Vec<typename A::out_t, N> ew_apply(const A &apply, const Vec<typename A::in1_t, N> &a, const Vec<typename A::in2_t, N> &b)
+{
+   if constexpr (has_vector_apply<A>::value && (N > 1)) {
+      return apply.template vec<N>(a, b);
+   } else {
+      Vec<typename A::out_t, N> o;
+#pragma unroll
+      for (int j = 0; j < N; j++) o.v[j] = apply(a.v[j], b.v[j]);
+      return o;
+   }
+}
+
 // Access to elements that do not start on a multiple of their size (only the copy
 // family accepts such tensors).  Loads fetch the aligned 32-bit words that cover
 // the bytes and realign them with a funnel shift; the word after the last one is
@@ -163,7 +185,7 @@ template <class T, int VEC, bool UNAL> SD_D void ew_store(char *p, const Vec<T, 
 
 // ---------------------------------------------------------------------------
 template <class A, bool UNAL>
-__global__ void __launch_bounds__(EW_THREADS) ew_contig(const A apply, const EwParams<A::NIN + 1> p)
+__global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig(const A apply, const EwParams<A::NIN + 1> p)
 {
    using X = ew_traits<A>;
    constexpr int VEC = X::VEC, U = X::UNROLL, NIN = X::NIN;
@@ -188,9 +210,7 @@ __global__ void __launch_bounds__(EW_THREADS) ew_contig(const A apply, const EwP
       for (int u = 0; u < U; u++) {
          uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
          if (i < nvec) {
-            Vec<out_t, VEC> o;
-#pragma unroll
-            for (int j = 0; j < VEC; j++) o.v[j] = apply(a[u].v[j], b[u].v[j]);
+            const Vec<out_t, VEC> o = ew_apply<A, VEC>(apply, a[u], b[u]);
             ew_store<out_t, VEC, UNAL>(po + i * (VEC * sizeof(out_t)), o, uo);
          }
       }
@@ -237,7 +257,7 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
       } else {
          uint64_t r = idx;
          for (int d = 0; d < p.ndims - 1; d++) {
-            uint64_t q = r / (uint64_t)p.size64[d];
+            uint64_t q = udiv64(r, (uint64_t)p.size64[d]);
             uint64_t c = r - q * (uint64_t)p.size64[d];
             r = q;
 #pragma unroll
@@ -249,9 +269,7 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
       Vec<in1_t, VEC> a; Vec<in2_t, VEC> b;
       if constexpr (NIN >= 1) a = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + off[0], VEC > 1 && b1, u1);
       if constexpr (NIN >= 2) b = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + off[1], VEC > 1 && b2, u2);
-      Vec<out_t, VEC> o;
-#pragma unroll
-      for (int j = 0; j < VEC; j++) o.v[j] = apply(a.v[j], b.v[j]);
+      const Vec<out_t, VEC> o = ew_apply<A, VEC>(apply, a, b);
       ew_store<out_t, VEC, UNAL>(p.ptr[NIN] + off[NIN], o, uo);
    }
 }

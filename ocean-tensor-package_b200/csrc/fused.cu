@@ -307,9 +307,22 @@ template <class C> SD_D void store_as(char *p, int dtype, C v, bool swap, bool u
 
 // Linear variant for one merged dimension: a block handles 256 x MR consecutive elements, a
 // thread MR of them 256 apart (coalesced), all loads issued before the first conversion.
-constexpr int M0 = 32;                      // tile extent along dimension 0
-constexpr int M1 = 64;                      // tile extent along dimension dt
-constexpr int MR = 8;                       // elements per thread (M0 * M1 / 256)
+// Tile of the tiled variant.  Measured on B200 (4096^2, f64 transposed x i32 byte-swapped + f32 row -> f32): the
+// shape (16x128, 32x64, 64x32) makes no difference, resident warps do: 3, 4, 5, 6 blocks of 256 threads per
+// multiprocessor ran at 78, 68, 62, 65 us, so the kernel is built for five (48 registers, a few spills).
+#ifndef MIX_M0
+#define MIX_M0 32
+#define MIX_M1 64
+#define MIX_NT 256
+#define MIX_BLOCKS 5
+#endif
+constexpr int M0 = MIX_M0;                  // tile extent along dimension 0
+constexpr int M1 = MIX_M1;                  // tile extent along dimension dt
+constexpr int MT = MIX_NT;                  // threads of a tile
+constexpr int MR = 8;                       // elements per thread and operand
+static_assert(M0 * M1 == MT * MR, "tile and thread count do not match");
+constexpr int MP1 = MT / M1;                // rows of dimension 0 per pass of phase 1
+constexpr int MP2 = MT / M0;                // rows of dimension dt per pass of phase 2
 
 template <class C>
 __global__ void __launch_bounds__(256) mix_linear(const MixParams p)
@@ -353,20 +366,21 @@ SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t
       const int tx = threadIdx.x & (M1 - 1), ty = threadIdx.x / M1;
       bool ok[MR];
 #pragma unroll
-      for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + ty + 4 * j < n0) && (it + tx < nt));
+      for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + ty + MP1 * j < n0) && (it + tx < nt));
       int slot = 0;
+#pragma unroll
       for (int k = 0; k < 3; k++) {
          if (!(p.staged & (1u << k))) continue;
          const char *q[MR];
          q[0] = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt] + (i0 + ty) * p.stride[k][0];
-         const int64_t step = 4 * p.stride[k][0];
+         const int64_t step = MP1 * p.stride[k][0];
 #pragma unroll
          for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
          uint64_t raw[MR]; C v[MR];
          load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
          bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
 #pragma unroll
-         for (int j = 0; j < MR; j++) tile[slot][ty + 4 * j][tx] = v[j];
+         for (int j = 0; j < MR; j++) tile[slot][ty + MP1 * j][tx] = v[j];
          slot++;
       }
       __syncthreads();
@@ -375,19 +389,20 @@ SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t
    const int tx = threadIdx.x & (M0 - 1), ty = threadIdx.x / M0;
    bool ok[MR];
 #pragma unroll
-   for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + tx < n0) && (it + ty + 8 * j < nt));
+   for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + tx < n0) && (it + ty + MP2 * j < nt));
    C acc[MR];
    int slot = 0;
-   for (int k = 0; k < 3; k++) {
+#pragma unroll
+   for (int k = 0; k < 3; k++) {                        // unrolled: k selects the arithmetic at compile time
       C v[MR];
       if (p.staged & (1u << k)) {
 #pragma unroll
-         for (int j = 0; j < MR; j++) v[j] = tile[slot][tx][ty + 8 * j];
+         for (int j = 0; j < MR; j++) v[j] = tile[slot][tx][ty + MP2 * j];
          slot++;
       } else {
          const char *q[MR];
          q[0] = p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0] + (it + ty) * p.stride[k][p.dt];
-         const int64_t step = 8 * p.stride[k][p.dt];
+         const int64_t step = MP2 * p.stride[k][p.dt];
 #pragma unroll
          for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
          uint64_t raw[MR];
@@ -399,24 +414,26 @@ SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t
    }
    char *qo[MR];
    qo[0] = p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0] + (it + ty) * p.stride[3][p.dt];
-   const int64_t ostep = 8 * p.stride[3][p.dt];
+   const int64_t ostep = MP2 * p.stride[3][p.dt];
 #pragma unroll
    for (int j = 1; j < MR; j++) qo[j] = qo[j - 1] + ostep;
    store_as_n<C, MR>(qo, ok, p.dtype[3], acc, p.swap[3], p.unal[3]);
 }
 
 template <class C>
-__global__ void __launch_bounds__(256, 4) mix_tiled(const MixParams p)
+__global__ void __launch_bounds__(MT, MIX_BLOCKS) mix_tiled(const MixParams p)
 {
    extern __shared__ __align__(16) unsigned char mix_smem[];
    C (*tile)[M0][M1 + 1] = reinterpret_cast<C (*)[M0][M1 + 1]>(mix_smem);
    uint64_t bid = blockIdx.x;
-   const uint64_t t0 = bid % p.tiles0; bid /= p.tiles0;
-   const uint64_t tt = bid % p.tilest; bid /= p.tilest;
+   uint64_t bq = udiv64(bid, p.tiles0);
+   const uint64_t t0 = bid - bq * p.tiles0; bid = bq;
+   bq = udiv64(bid, p.tilest);
+   const uint64_t tt = bid - bq * p.tilest; bid = bq;
    int64_t off[4] = {0, 0, 0, 0};
    for (int d = 1; d < p.ndims; d++) {
       if (d == p.dt) continue;
-      uint64_t q = bid / (uint64_t)p.size[d]; uint64_t c = bid - q * (uint64_t)p.size[d]; bid = q;
+      uint64_t q = udiv64(bid, (uint64_t)p.size[d]); uint64_t c = bid - q * (uint64_t)p.size[d]; bid = q;
 #pragma unroll
       for (int k = 0; k < 4; k++) off[k] += (int64_t)c * p.stride[k][d];
    }
@@ -480,11 +497,10 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
          SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * M0 * (M1 + 1) * (int)sizeof(C)));
          attr_set[sizeof(C) == 8] = true;
       }
-      mix_tiled<C><<<(unsigned)blocks, 256, smem, stream>>>(p);
+      mix_tiled<C><<<(unsigned)blocks, MT, smem, stream>>>(p);
    } else {
       uint64_t blocks = (p.nelem + 256ull * MR - 1) / (256ull * MR);
-      uint64_t cap = (uint64_t)dev.sms * (dev.max_threads_per_sm / 256) * 4;
-      if (blocks > cap) blocks = cap;
+      if (blocks > 0x7FFFFFFFull) blocks = 0x7FFFFFFFull;            // one chunk per block
       mix_linear<C><<<(unsigned)blocks, 256, 0, stream>>>(p);
    }
    SD_LAUNCH_CHECK();

@@ -62,7 +62,7 @@ SD_D void outer_offsets(const RedParams &p, uint64_t o, int64_t &off1, int64_t &
 {
    off1 = 0; off2 = 0;
    for (int d = 0; d < p.ndims - 1; d++) {
-      uint64_t q = o / (uint64_t)p.size[d]; uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
+      uint64_t q = udiv64(o, (uint64_t)p.size[d]); uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
       off1 += (int64_t)c * p.stride1[d]; off2 += (int64_t)c * p.stride2[d];
    }
    if (p.ndims > 0) { off1 += (int64_t)o * p.stride1[p.ndims - 1]; off2 += (int64_t)o * p.stride2[p.ndims - 1]; }
@@ -72,7 +72,7 @@ SD_D int64_t reduced_offset(const RedParams &p, uint64_t r, int first)
 {
    int64_t off = 0;
    for (int d = first; d < p.rdims - 1; d++) {
-      uint64_t q = r / (uint64_t)p.rsize[d]; uint64_t c = r - q * (uint64_t)p.rsize[d]; r = q;
+      uint64_t q = udiv64(r, (uint64_t)p.rsize[d]); uint64_t c = r - q * (uint64_t)p.rsize[d]; r = q;
       off += (int64_t)c * p.rstride[d];
    }
    if (p.rdims > first) off += (int64_t)r * p.rstride[p.rdims - 1];
@@ -212,7 +212,7 @@ __global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedPa
    const uint32_t gpb = RED_THREADS / group;
    const uint64_t gid = (uint64_t)blockIdx.x * gpb + threadIdx.x / group;
    const uint32_t lane = threadIdx.x % group;
-   const uint64_t out = gid / p.split;
+   const uint64_t out = udiv64(gid, p.split);
    const uint32_t s = (uint32_t)(gid - out * p.split);
    const bool live = out < p.nout;
 
@@ -224,12 +224,12 @@ __global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedPa
    if (live) {
       const uint64_t rowlen = (uint64_t)p.rsize[0];
       const uint64_t nslot = (rowlen + VEC - 1) / VEC;              // vector slots per row (last may be ragged)
-      const uint64_t rows = p.relem / rowlen;
+      const uint64_t rows = udiv64(p.relem, rowlen);
       const uint64_t total = rows * nslot;
       constexpr int U = sizeof(T) >= 4 ? 8 : 4;         // vectors in flight per thread (measured: 8 is slower for 1-byte types)
       // slots per split, rounded up to whole iterations of the dense loop (trailing splits may be empty)
-      uint64_t chunk = (total + p.split - 1) / p.split;
-      chunk = (chunk + (uint64_t)group * U - 1) / ((uint64_t)group * U) * ((uint64_t)group * U);
+      uint64_t chunk = udiv64(total + p.split - 1, p.split);
+      chunk = udiv64(chunk + (uint64_t)group * U - 1, (uint64_t)group * U) * ((uint64_t)group * U);
       const uint64_t begin = (uint64_t)s * chunk < total ? (uint64_t)s * chunk : total;
       const uint64_t end = begin + chunk < total ? begin + chunk : total;
       uint64_t slot0 = begin + lane;
@@ -258,7 +258,7 @@ __global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedPa
             cnt[u] = 0;
             if (slot < end) {
                uint64_t row = 0, j = slot;
-               if (rows > 1) { row = slot / nslot; j = slot - row * nslot; }
+               if (rows > 1) { row = udiv64(slot, nslot); j = slot - row * nslot; }
                const char *q = base + (rows > 1 ? reduced_offset(p, row, 1) : 0) + (int64_t)(j * VEC * sizeof(T));
                uint64_t left = rowlen - j * VEC;
                if (VEC == 1 || left >= (uint64_t)VEC) { v[u] = ld_vec<T, VEC>(q); cnt[u] = VEC; }
@@ -305,8 +305,9 @@ __global__ void __launch_bounds__(RED_THREADS, RED_MIN_BLOCKS(T)) red_col(const 
    using A = typename R::acc_t;
    __shared__ A smem[RED_THREADS][VEC];                                  // [y * blockDim.x + x]
    uint64_t bid = blockIdx.x;
-   const uint32_t s = (uint32_t)(bid % p.split); bid /= p.split;
-   const uint64_t tile = bid % p.tiles0; const uint64_t rest = bid / p.tiles0;
+   const uint64_t bq = udiv64(bid, p.split);
+   const uint32_t s = (uint32_t)(bid - bq * p.split); bid = bq;
+   const uint64_t rest = udiv64(bid, p.tiles0); const uint64_t tile = bid - rest * p.tiles0;
    const uint64_t o0 = (tile * blockDim.x + threadIdx.x) * VEC;         // first of my outputs along dim 0
    const bool live = o0 < (uint64_t)p.size[0];
    const int nmine = live ? (int)(((uint64_t)p.size[0] - o0) < (uint64_t)VEC ? ((uint64_t)p.size[0] - o0) : VEC) : 0;
@@ -315,7 +316,7 @@ __global__ void __launch_bounds__(RED_THREADS, RED_MIN_BLOCKS(T)) red_col(const 
    int64_t off1 = 0, off2 = 0;
    {  uint64_t o = rest;
       for (int d = 1; d < p.ndims - 1; d++) {
-         uint64_t q = o / (uint64_t)p.size[d]; uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
+         uint64_t q = udiv64(o, (uint64_t)p.size[d]); uint64_t c = o - q * (uint64_t)p.size[d]; o = q;
          off1 += (int64_t)c * p.stride1[d]; off2 += (int64_t)c * p.stride2[d]; }
       if (p.ndims > 1) { off1 += (int64_t)o * p.stride1[p.ndims - 1]; off2 += (int64_t)o * p.stride2[p.ndims - 1]; }
    }
@@ -324,7 +325,7 @@ __global__ void __launch_bounds__(RED_THREADS, RED_MIN_BLOCKS(T)) red_col(const 
 #pragma unroll
    for (int e = 0; e < VEC; e++) acc[e] = red_start<R, T>(r, (e < nmine) ? base + e * sizeof(T) : p.src);
 
-   const uint64_t chunk = (p.relem + p.split - 1) / p.split;
+   const uint64_t chunk = udiv64(p.relem + p.split - 1, p.split);
    const uint64_t begin = (uint64_t)s * chunk;
    const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
    if (live) {
@@ -404,14 +405,14 @@ __global__ void __launch_bounds__(RED_THREADS) red_gen(const R r, const RedParam
 {
    using A = typename R::acc_t;
    const uint64_t gid = (uint64_t)blockIdx.x * RED_THREADS + threadIdx.x;
-   const uint64_t out = gid / p.split;
+   const uint64_t out = udiv64(gid, p.split);
    const uint32_t s = (uint32_t)(gid - out * p.split);
    if (out >= p.nout) return;
    int64_t off1, off2;
    outer_offsets(p, out, off1, off2);
    const char *base = p.src + off1;
    A acc = red_start<R, T>(r, base);
-   const uint64_t chunk = (p.relem + p.split - 1) / p.split;
+   const uint64_t chunk = udiv64(p.relem + p.split - 1, p.split);
    const uint64_t begin = (uint64_t)s * chunk;
    const uint64_t end = begin + chunk < p.relem ? begin + chunk : p.relem;
    for (uint64_t rr = begin; rr < end; rr++) r.accum(acc, ld_one<T>(base + reduced_offset(p, rr, 0)));

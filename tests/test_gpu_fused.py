@@ -149,3 +149,31 @@ def test_device_resident_reduction_matches_host_returning_form(gpu):
         from solid_b200 import oplist as ol
         k = dt.SIZE[ol.reduce_result_type(op, dtype)]
         assert bytes(dev.download(res)[:k]) == host[:k], (dtype, op)
+
+
+def test_axpy_half_every_pattern(gpu, cpu):
+    """Half axpy takes a vector-wide shortcut while all products and sums stay in the normal half range and
+    falls back per vector otherwise: run every half bit pattern as x against scalars and addends that keep
+    most vectors on the shortcut (ordinary magnitudes), push them to its edges (tiny and huge scalars,
+    cancelling addends) or leave it (zeros, infinities, NaNs)."""
+    dev = util.Device()
+    rng = np.random.default_rng(81)
+    n = 1 << 16
+    x = np.arange(n, dtype=np.uint16)
+    addends = {
+        "ordinary": (rng.integers(0x3000, 0x4800, n) | (rng.integers(0, 2, n) << 15)).astype(np.uint16),   # 0.125 .. 8, both signs
+        "cancelling": (x ^ 0x8000).astype(np.uint16),                                                        # y = -x
+        "any": rng.permutation(n).astype(np.uint16),
+        "zero": np.zeros(n, dtype=np.uint16),
+    }
+    for a_bits in (0x3800, 0x3C01, 0xC200, 0x1400, 0x63D0, 0x0000, 0x7C00):    # 0.5, 1+ulp, -3, 2^-10, 1000, 0, inf
+        a = np.array([a_bits], dtype=np.uint16)
+        for name, y in addends.items():
+            t, want = np.zeros(n, dtype=np.uint16), np.zeros(n, dtype=np.uint16)
+            cpu.binary("multiply", "half", [n], [2], x.ctypes.data, [0], a.ctypes.data, [2], t.ctypes.data)
+            cpu.binary("add", "half", [n], [2], t.ctypes.data, [2], y.ctypes.data, [2], want.ctypes.data)
+            dx, dy, dz = dev.upload(x.view(np.uint8)), dev.upload(y.view(np.uint8)), dev.empty(2 * n)
+            gpu.axpy("half", [n], a.tobytes(), [2], dx.data_ptr(), [2], dy.data_ptr(), [2], dz.data_ptr(), dev.stream)
+            got = dev.download(dz)[: 2 * n].view(np.uint16)
+            bad = np.nonzero(got != want)[0]
+            assert bad.size == 0, (hex(a_bits), name, [(hex(x[i]), hex(y[i]), hex(got[i]), hex(want[i])) for i in bad[:5]])
