@@ -522,9 +522,9 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": "of " + peak_kind, "kernel": "axpy_sums_kernel<float>",
                          "kernel_ms": kernel_ms,
-                         # dram__bytes_read + dram__bytes_write of one launch: 3.187 GB measured by ncu at 2^28
+                         # dram__bytes_read + dram__bytes_write of one launch: 3.184 GB measured by ncu at 2^28
                          # elements (profiles/axpy_sums_kernel_float_c5.md), proportional to the element count
-                         "traffic": 3.187e9 * per / float(1 << 28), "traffic_unit": "bytes per launch"},
+                         "traffic": 3.184e9 * per / float(1 << 28), "traffic_unit": "bytes per launch"},
             "e2e": {"value": BYTES_PER_ELEMENT * n_total / (e2e_ms * 1e-3) / 1e9, "unit": "GB/s",
                     "h2d_bytes_per_step": 8 * per, "d2h_bytes_per_step": 8, "ms_per_step": e2e_ms,
                     "note": "per rank; inputs streamed through 256 MiB pinned windows (double buffered), z stays on the device"},
