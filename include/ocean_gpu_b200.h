@@ -75,6 +75,16 @@ OCGPU_UNARY_OPS(OCGPU_DECLARE_UNARY_)
    SOLID_API int OcTensorGPU_##OP(const OcTensorView *src1, const OcTensorView *src2, const OcTensorView *dst);
 OCGPU_BINARY_OPS(OCGPU_DECLARE_BINARY_)
 
+/* Tensor (op) scalar with the scalar passed by value: the forms behind OcTensor_addScalar, _subtractScalar,      */
+/* _multiplyScalar and _bitwise{And,Or,Xor}Scalar (src/core/interface/tensor_itf.c:4215-4251), which the reference */
+/* runs as tensor operations on a 0-d device tensor built from the scalar.  The scalar must have the tensor's dtype. */
+#define OCGPU_SCALAR_OPS(X) \
+   X(addScalar, add_scalar) X(subtractScalar, subtract_scalar) X(multiplyScalar, multiply_scalar) \
+   X(bitwiseAndScalar, bitwise_and_scalar) X(bitwiseOrScalar, bitwise_or_scalar) X(bitwiseXorScalar, bitwise_xor_scalar)
+#define OCGPU_DECLARE_SCALAR_(OP, SOLID) \
+   SOLID_API int OcTensorGPU_##OP(const OcTensorView *src, const OcScalarView *scalar, const OcTensorView *dst);
+OCGPU_SCALAR_OPS(OCGPU_DECLARE_SCALAR_)
+
 SOLID_API int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst);
 SOLID_API int OcTensorGPU_byteswapNoFlag(const OcTensorView *tensor);   /* reverses the stored bytes in place */
 SOLID_API int OcTensorGPU_fill(const OcTensorView *tensor, const OcScalarView *scalar);

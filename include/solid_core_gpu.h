@@ -85,6 +85,15 @@
    X(bitshift_left, integer_bool) X(bitshift_right, integer_bool) \
    X(power, all)
 
+/* Binary operations with the second operand a scalar passed BY VALUE: dst = op(src, value).      */
+/* No counterpart in the reference's Solid layer: Ocean's addScalar, subtractScalar, multiplyScalar */
+/* and bitwise{And,Or,Xor}Scalar build a 0-d device tensor from the scalar and call the tensor     */
+/* operation (src/core/interface/tensor_itf.c:4215-4251, "Possible optimization"); these entry     */
+/* points skip that tensor.  Results are those of the tensor operation with a broadcast operand.   */
+#define SOLID_GPU_SCALAR_OPS(X) \
+   X(add_scalar, all) X(subtract_scalar, all) X(multiply_scalar, all) \
+   X(bitwise_and_scalar, integer_bool) X(bitwise_or_scalar, integer_bool) X(bitwise_xor_scalar, integer_bool)
+
 /* Global reductions -- .src:293-366.  `result` is a HOST pointer, `buffer` device scratch */
 /* of at least solid_gpu_reduce_all_buffer_size() bytes.                                   */
 #define SOLID_GPU_REDUCE_BOOL_OPS(X)   /* (..., solid_bool *result, buffer, stream) */ \
@@ -131,6 +140,14 @@
    int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, \
    const ptrdiff_t *strides2, void *ptr2, const ptrdiff_t *strides3, void *ptr3, \
    cudaStream_t stream
+#define SOLID_GPU_ARGS_SCALAR_OP \
+   int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, \
+   const solid_scalar value, const ptrdiff_t *strides2, void *ptr2, cudaStream_t stream
+#define SOLID_GPU_ARGS_STEPS_HEAD \
+   int ndims, const size_t *size, const ptrdiff_t *strides, void *ptr
+#define SOLID_GPU_ARGS_STEPS_INT64   SOLID_GPU_ARGS_STEPS_HEAD, solid_int64 offset, solid_int64 step, cudaStream_t stream
+#define SOLID_GPU_ARGS_STEPS_DOUBLE  SOLID_GPU_ARGS_STEPS_HEAD, solid_double offset, solid_double step, cudaStream_t stream
+#define SOLID_GPU_ARGS_STEPS_CDOUBLE SOLID_GPU_ARGS_STEPS_HEAD, solid_cdouble offset, solid_cdouble step, cudaStream_t stream
 #define SOLID_GPU_ARGS_COPY \
    int ndims1, const size_t *size1, const ptrdiff_t *strides1, void *ptr1, \
    int ndims2, const size_t *size2, const ptrdiff_t *strides2, void *ptr2, \
@@ -179,6 +196,24 @@ SOLID_GPU_UNARY_OPS(SOLID_GPU_DECLARE_)
 
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_BINARY
 SOLID_GPU_BINARY_OPS(SOLID_GPU_DECLARE_)
+#undef SOLID_GPU_ARGS_CURRENT_
+
+/* Ranges: element i (column-major position in the tensor's own dimensions) = offset + i * step, evaluated */
+/* in int64, double or complex double and cast to the element type -- solid_core_gpu.src:61-68,            */
+/* template_steps.cu:30-122.  steps_cdouble exists for the complex types only, as in the reference.       */
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_STEPS_INT64
+SOLID_GPU_DECLARE_(steps_int64, all)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_STEPS_DOUBLE
+SOLID_GPU_DECLARE_(steps_double, all)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_STEPS_CDOUBLE
+SOLID_GPU_DECLARE_(steps_cdouble, complex)
+#undef SOLID_GPU_ARGS_CURRENT_
+
+/* strides2 == NULL and ptr2 == NULL: in place */
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_SCALAR_OP
+SOLID_GPU_SCALAR_OPS(SOLID_GPU_DECLARE_)
 #undef SOLID_GPU_ARGS_CURRENT_
 
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_REDUCE_BOOL

@@ -11,6 +11,35 @@
 
 SOLID_GPU_BINARY_OPS(SD_DEFINE_BINARY)
 
+// dst = op(src, value) with the scalar in the launch arguments (list: SOLID_GPU_SCALAR_OPS); the same
+// functors as the tensor operations, so the results are those of a broadcast second operand.
+namespace sd {
+template <class Op, class T> struct ScalarApply {
+   static constexpr int NIN = 1;
+   using in1_t = T; using in2_t = Nothing; using out_t = typename Op::template out<T>;
+   T s;
+   SD_D out_t operator()(T x, Nothing) const { return Op::template f<T>(x, s); }
+};
+template <class Op, class T>
+int launch_scalar(int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, const solid_scalar &value,
+                  const ptrdiff_t *strides2, void *ptr2, cudaStream_t stream)
+{
+   if (strides2 == nullptr && ptr2 == nullptr) { strides2 = strides1; ptr2 = ptr1; }   // in place
+   const ptrdiff_t *st[2] = { strides1, strides2 }; void *pt[2] = { ptr1, ptr2 };
+   Layout<2> L;
+   if (make_layout<2>(L, ndims, size, st, pt, 1) != 0) return -1;
+   ScalarApply<Op, T> ap; memcpy(&ap.s, &value, sizeof(T));
+   return ew_launch(ap, L, stream);
+}
+} // namespace sd
+#define SD_DEFINE_SCALAR(NAME, OP, GROUP) SD_WHEN(GROUP)(                                          \
+   extern "C" int SD_PASTE(solid_gpu_##NAME##_, SDX)(SOLID_GPU_ARGS_SCALAR_OP)                      \
+   {  return sd::launch_scalar<sd::b_##OP, T>(ndims, size, strides1, ptr1, value, strides2, ptr2, stream); })
+SD_DEFINE_SCALAR(add_scalar, add, all) SD_DEFINE_SCALAR(subtract_scalar, subtract, all)
+SD_DEFINE_SCALAR(multiply_scalar, multiply, all)
+SD_DEFINE_SCALAR(bitwise_and_scalar, bitwise_and, integer_bool) SD_DEFINE_SCALAR(bitwise_or_scalar, bitwise_or, integer_bool)
+SD_DEFINE_SCALAR(bitwise_xor_scalar, bitwise_xor, integer_bool)
+
 // z = a*x + y with the product rounded to the element type first: what Ocean's
 // multiplyScalar followed by add produces (src/core/interface/tensor_itf.c:4221-4251),
 // in one pass.  Real floating-point types.

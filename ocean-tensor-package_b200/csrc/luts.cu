@@ -22,6 +22,10 @@ SOLID_GPU_FILL_OPS(SD_DEFINE_LUT)
 SD_DEFINE_LUT(masked_fill, all)
 SOLID_GPU_UNARY_OPS(SD_DEFINE_LUT)
 SOLID_GPU_BINARY_OPS(SD_DEFINE_LUT)
+SOLID_GPU_SCALAR_OPS(SD_DEFINE_LUT)
+SD_DEFINE_LUT(steps_int64, all)
+SD_DEFINE_LUT(steps_double, all)
+SD_DEFINE_LUT(steps_cdouble, complex)
 SOLID_GPU_REDUCE_BOOL_OPS(SD_DEFINE_LUT)
 SOLID_GPU_REDUCE_BOUND1_OPS(SD_DEFINE_LUT)
 SOLID_GPU_REDUCE_BOUND2_OPS(SD_DEFINE_LUT)

@@ -195,6 +195,25 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *src1, const OcTensorView *sr
 }
 OCGPU_BINARY_OPS(OCGPU_DEFINE_BINARY)
 
+// ---------------------------------------------------------------------------------- tensor (op) scalar
+#define OCGPU_DEFINE_SCALAR(OP, SOLID)                                                             \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *src, const OcScalarView *scalar, const OcTensorView *dst) \
+{                                                                                                  \
+   if (check_elemwise(src, "source") != 0 || check_elemwise(dst, "destination") != 0) return -1;   \
+   if (scalar == nullptr) return fail("Missing scalar in " #OP);                                   \
+   if (!same_shape(src, dst)) return fail("Tensor size mismatch in " #OP);                         \
+   if (scalar->dtype != src->dtype || dst->dtype != src->dtype) return fail("Data type mismatch in " #OP); \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   if (f == nullptr) return -1;                                                                    \
+   if (set_device(dst->device) != 0) return -1;                                                    \
+   if (start_read(dst, src) != 0) return -1;                                                       \
+   if (f(dst->ndims, dst->size, src->strides, src->data, scalar->value,                            \
+         dst->strides, dst->data, dst->stream) != 0) return fail_solid();                          \
+   if (update(dst) != 0) return -1;                                                                \
+   return finish_read(dst, src);                                                                   \
+}
+OCGPU_SCALAR_OPS(OCGPU_DEFINE_SCALAR)
+
 // ---------------------------------------------------------------------------------- copy / fill
 extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst)
 {

@@ -60,6 +60,11 @@ def _strides(seq):
     return (C.c_ssize_t * max(len(seq), 1))(*seq)
 
 
+class CDouble(C.Structure):
+    """solid_cdouble, passed by value to the steps_cdouble functions."""
+    _fields_ = [("real", C.c_double), ("imag", C.c_double)]
+
+
 def scalar_from_bytes(raw: bytes) -> Scalar:
     s = Scalar()
     C.memmove(C.addressof(s), raw, min(len(raw), 16))
@@ -120,6 +125,26 @@ class SolidGPU:
         self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
                       _strides(strides2), C.c_void_p(ptr2), _strides(strides3), C.c_void_p(ptr3),
                       C.c_void_p(stream)), "%s_%s" % (name, dtype))
+
+    def scalar_op(self, name, dtype, size, strides1, ptr1, value: bytes, strides2, ptr2, stream=0):
+        """dst = op(src, value) with the scalar passed by value; name is 'add', 'subtract', 'multiply',
+        'bitwise_and', 'bitwise_or' or 'bitwise_xor'."""
+        f = self.fn("solid_gpu_%s_scalar_%s" % (name, dtype))
+        st2 = _strides(strides2) if strides2 is not None else None          # None, None: in place
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1), scalar_from_bytes(value),
+                      st2, C.c_void_p(ptr2), C.c_void_p(stream)), "%s_scalar_%s" % (name, dtype))
+
+    def steps(self, kind, dtype, size, strides, ptr, offset, step, stream=0):
+        """tensor[i] = offset + i * step; kind is 'int64', 'double' or 'cdouble' (complex element types only)."""
+        f = self.fn("solid_gpu_steps_%s_%s" % (kind, dtype))
+        if kind == "int64":
+            args = (C.c_int64(int(offset)), C.c_int64(int(step)))
+        elif kind == "double":
+            args = (C.c_double(float(offset)), C.c_double(float(step)))
+        else:
+            args = (CDouble(complex(offset).real, complex(offset).imag), CDouble(complex(step).real, complex(step).imag))
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), *args, C.c_void_p(stream)),
+                    "steps_%s_%s" % (kind, dtype))
 
     def axpy(self, dtype, size, a: bytes, strides1, ptr1, strides2, ptr2, strides3, ptr3, stream=0):
         f = self.fn("solid_gpu_axpy_%s" % dtype)

@@ -22,6 +22,10 @@ BINARY_OPS = {
     "bitshift_left": "integer_bool", "bitshift_right": "integer_bool", "power": "all",
 }
 COMPARE_OPS = ["lt", "le", "ge", "gt", "eq", "ne"]
+STEPS_OPS = {"steps_int64": "all", "steps_double": "all", "steps_cdouble": "complex"}
+# second operand passed by value (solid_gpu_<op>_scalar_<type>)
+SCALAR_OPS = {"add": "all", "subtract": "all", "multiply": "all",
+              "bitwise_and": "integer_bool", "bitwise_or": "integer_bool", "bitwise_xor": "integer_bool"}
 REDUCE_BOOL_OPS = {"any": "all", "all": "all", "all_finite": "float", "any_inf": "float", "any_nan": "float"}
 REDUCE_BOUND1_OPS = {"all_lt": "all", "all_le": "all", "all_gt": "all", "all_ge": "all"}
 REDUCE_BOUND2_OPS = {"all_gtlt": "all", "all_gtle": "all", "all_gelt": "all", "all_gele": "all"}

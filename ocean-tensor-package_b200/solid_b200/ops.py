@@ -230,6 +230,23 @@ def binary(name: str, a: Tensor, b: Tensor, dst: Tensor | None = None) -> Tensor
     return out
 
 
+def scalar_op(name: str, a: Tensor, value, dst: Tensor | None = None) -> Tensor:
+    """Tensor (op) Python scalar in the tensor's own type with the scalar passed by value (Ocean's
+    addScalar, subtractScalar, multiplyScalar, bitwise{And,Or,Xor}Scalar without the 0-d device tensor)."""
+    if name not in ol.SCALAR_OPS or a.dtype not in dt.GROUPS[ol.SCALAR_OPS[name]]:
+        raise TypeError("%s with a scalar is not available for type %s" % (name, a.dtype))
+    x = _native(a)
+    out = dst if (dst is not None and dst.dtype == a.dtype and not dst.byteswapped and dst.size == a.size) \
+        else Tensor.empty(a.size, a.dtype, a.storage.device)
+    sv = _ocean.get().scalar(scalar_bytes(value, a.dtype), a.dtype)
+    import ctypes as C
+    _dispatch(_ocean.ocean_name(name) + "Scalar" if name != "multiply" else "multiplyScalar", x, C.byref(sv), out)
+    if dst is not None and out is not dst:
+        copy(out, dst)
+        return dst
+    return out
+
+
 def add(a, b, dst=None):
     return binary("add", a, b, dst)
 

@@ -39,6 +39,10 @@ def _scalar(raw: bytes) -> Scalar:
     return s
 
 
+class CDouble(C.Structure):
+    _fields_ = [("real", C.c_double), ("imag", C.c_double)]
+
+
 class SolidCPU:
     def __init__(self, path=LIB_PATH):
         if not Path(path).exists():
@@ -87,6 +91,17 @@ class SolidCPU:
         self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(
             C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1),
             _strides(strides2), C.c_void_p(ptr2), _strides(strides3), C.c_void_p(ptr3)), name)
+
+    def steps(self, kind, dtype, size, strides, ptr, offset, step):
+        """solid_cpu_steps_<kind>_<dtype> (solid/src/core/cpu/template_steps.c); kind 'int64', 'double', 'cdouble'."""
+        f = self.fn("solid_cpu_steps_%s_%s" % (kind, dtype))
+        if kind == "int64":
+            args = (C.c_int64(int(offset)), C.c_int64(int(step)))
+        elif kind == "double":
+            args = (C.c_double(float(offset)), C.c_double(float(step)))
+        else:
+            args = (CDouble(complex(offset).real, complex(offset).imag), CDouble(complex(step).real, complex(step).imag))
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), *args), "steps")
 
     def byteswap(self, dtype, size, strides, ptr):
         self._check(self.fn("solid_cpu_byteswap_%s" % dtype)(

@@ -250,3 +250,39 @@ def test_fill_and_masked_fill(dtype, gpu, cpu):
         d = dev.upload(buf)
         gpu.fill("fill_nan", dtype, v.size, v.strides, d.data_ptr(), value, dev.stream)
         assert np.array_equal(dev.download(d), want), "fill_nan_%s" % dtype
+
+
+@pytest.mark.parametrize("op", sorted(ol.SCALAR_OPS))
+def test_scalar_operand_by_value_matches_broadcast_tensor(op, gpu, cpu):
+    """solid_gpu_<op>_scalar_<type> takes the second operand by value; the oracle is the reference's tensor
+    operation with that scalar as a stride-0 second operand (what Ocean's addScalar and relatives run).
+    Bit-exact, including the in-place form (no destination given)."""
+    dev = util.Device()
+    for dtype in dt.GROUPS[ol.SCALAR_OPS[op]]:
+        rng = np.random.default_rng(zlib.crc32(("%s %s s" % (op, dtype)).encode()))
+        kind = "small" if (dtype in dt.GROUPS["integer"] and op == "multiply") else \
+               ("special" if dtype in dt.GROUPS["float"] else "general")
+        es = dt.SIZE[dtype]
+        for name, size, v1, vout in layouts(dtype):
+            if name in ("row_broadcast", "scalar_broadcast"):
+                continue                                # a source that overlaps itself cannot be updated in place
+            a = util.fill_buffer(v1, rng, kind)
+            s = util.random_values(dtype, 1, rng, kind)
+            sbuf = np.zeros(64, dtype=np.uint8); sbuf[:es] = s.view(np.uint8)[:es]
+            zero = [0] * len(size)
+            for in_place in (False, True):
+                vo = v1 if in_place else vout
+                dst0 = a.copy() if in_place else util.fill_buffer(vout, rng, "general")
+                want = dst0.copy()
+                src = want if in_place else a
+                cpu.binary(op, dtype, size, v1.strides, src.ctypes.data + v1.offset, zero, sbuf.ctypes.data,
+                           vo.strides, want.ctypes.data + vo.offset)
+                da, dd = dev.upload(a), dev.upload(dst0)
+                if in_place:
+                    gpu.scalar_op(op, dtype, size, v1.strides, dd.data_ptr() + v1.offset, sbuf[:es].tobytes(), None, None, dev.stream)
+                else:
+                    gpu.scalar_op(op, dtype, size, v1.strides, da.data_ptr() + v1.offset, sbuf[:es].tobytes(),
+                                  vo.strides, dd.data_ptr() + vo.offset, dev.stream)
+                got = dev.download(dd)
+                util.assert_same(util.gather(got, vo), util.gather(want, vo), dtype, 0,
+                                 "%s_scalar_%s %s%s" % (op, dtype, name, " in place" if in_place else ""))

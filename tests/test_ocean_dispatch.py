@@ -117,6 +117,35 @@ def test_results_and_scratch_cache_rotation(gpu):
 
 
 @pytest.mark.gpu
+def test_scalar_forms_equal_tensor_forms(gpu):
+    """OcTensorGPU_addScalar and relatives (scalar by value) against the tensor operation with a 0-d operand,
+    which is how the reference runs them; also into a transposed destination and with a mismatched scalar type."""
+    from solid_b200 import Tensor, ops, dtypes as dt
+    import ctypes as C
+    _ocean.get().init()
+    rng = np.random.default_rng(5)
+    x = rng.normal(size=(37, 11)).astype(np.float32)
+    t = Tensor.from_numpy(np.asfortranarray(x))
+    s0 = Tensor.from_numpy(np.array(1.75, dtype=np.float32))
+    for name, fn in (("add", ops.add), ("subtract", ops.subtract), ("multiply", ops.scale)):
+        assert np.array_equal(ops.scalar_op(name, t, 1.75).numpy(), fn(t, s0).numpy()), name
+    k = rng.integers(-1000, 1000, 501).astype(np.int16)
+    tk = Tensor.from_numpy(k)
+    for name, ref in (("bitwise_and", k & 0x0F0F), ("bitwise_or", k | 0x0F0F), ("bitwise_xor", k ^ 0x0F0F)):
+        assert np.array_equal(ops.scalar_op(name, tk, 0x0F0F).numpy(), ref), name
+    out = Tensor.empty([11, 37], "float").T
+    ops.scalar_op("multiply", t, -2.0, out)
+    assert np.array_equal(out.numpy(), x * np.float32(-2.0))
+    with pytest.raises(TypeError):
+        ops.scalar_op("bitwise_and", t, 3)
+    oc = _ocean.get()
+    bad = oc.scalar(b"\0" * 8, "double")
+    v = oc.view(t, 0)
+    with pytest.raises(_ocean.OceanError, match="type mismatch"):
+        oc._check(oc.fn("addScalar")(C.byref(v), C.byref(bad), C.byref(v)), "addScalar")
+
+
+@pytest.mark.gpu
 def test_stream_protocol_orders_producer_and_consumer(gpu):
     """The source is produced on one stream, the operation runs on the destination's stream: the
     dispatch must wait for the source's event, and record the destination's."""
