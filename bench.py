@@ -282,6 +282,13 @@ def ops_table(peak: float, with_cpu: bool, only=None, iters_scale: float = 1.0):
             add_row("C1", name + " f32 2^24", 12 * n,
                     lambda name=name: (lambda i: ops.binary(name, xs[i], ys[i], zs[i]))(rot()),
                     (lambda name=name: cpu.binary(name, "float", [n], [4], hx[0].ctypes.data, [4], hy[0].ctypes.data, [4], hz.ctypes.data)) if cpu else None)
+        # the scalar operand by value (Ocean's multiplyScalar without its 0-d device tensor) and a range
+        add_row("C1", "multiply by a scalar (by value) f32 2^24", 8 * n,
+                lambda: (lambda i: ops.scalar_op("multiply", xs[i], 0.5, zs[i]))(rot()),
+                (lambda: cpu.binary("multiply", "float", [n], [4], hx[0].ctypes.data, [0], hy[0].ctypes.data, [4], hz.ctypes.data)) if cpu else None)
+        add_row("C1", "range offset + i*step (steps_double) f32 2^24", 4 * n,
+                lambda: (lambda i: lib.steps("double", "float", [n], [4], zs[i].ptr, -1.0, 1e-3, cur))(rot()),
+                (lambda: cpu.steps("double", "float", [n], [4], hz.ctypes.data, -1.0, 1e-3)) if cpu else None)
         for name in ("sum", "norm2", "maximum"):
             add_row("C1", name + " f32 2^24 (incl. host read-back)", 4 * n,
                     lambda name=name: ops.reduce_all(name, xs[rot()]),

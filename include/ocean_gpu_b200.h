@@ -85,6 +85,13 @@ OCGPU_BINARY_OPS(OCGPU_DECLARE_BINARY_)
    SOLID_API int OcTensorGPU_##OP(const OcTensorView *src, const OcScalarView *scalar, const OcTensorView *dst);
 OCGPU_SCALAR_OPS(OCGPU_DECLARE_SCALAR_)
 
+/* Ranges (src/core/gpu/op/tensor_steps_gpu.c:52-140): element i = offset + i * step.  As in the reference the  */
+/* tensor is first reduced to its memory layout (unit and zero-stride dimensions dropped, negative strides made   */
+/* positive, dimensions sorted by stride and merged: OcSolid_analyzeElemwise1), so i counts in memory order.      */
+SOLID_API int OcTensorGPU_stepsInt64(const OcTensorView *tensor, solid_int64 offset, solid_int64 step);
+SOLID_API int OcTensorGPU_stepsDouble(const OcTensorView *tensor, solid_double offset, solid_double step);
+SOLID_API int OcTensorGPU_stepsCDouble(const OcTensorView *tensor, solid_cdouble offset, solid_cdouble step);
+
 SOLID_API int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst);
 SOLID_API int OcTensorGPU_byteswapNoFlag(const OcTensorView *tensor);   /* reverses the stored bytes in place */
 SOLID_API int OcTensorGPU_fill(const OcTensorView *tensor, const OcScalarView *scalar);

@@ -7,6 +7,7 @@
 #include <cstdarg>
 #include <cstring>
 #include <mutex>
+#include <utility>
 #include "ocean_gpu_b200.h"
 
 namespace {
@@ -213,6 +214,48 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *src, const OcScalarView *sca
    return finish_read(dst, src);                                                                   \
 }
 OCGPU_SCALAR_OPS(OCGPU_DEFINE_SCALAR)
+
+// ---------------------------------------------------------------------------------- ranges
+// The memory layout of one tensor (OcSolid_analyzeElemwise1, src/external/ocean-solid/ocean_solid.c:85-130):
+// no unit or repeated dimensions, positive strides in increasing order, contiguous neighbours merged.
+struct Analyzed { int ndims; size_t size[8]; ptrdiff_t strides[8]; char *ptr; };
+static void analyze1(const OcTensorView *t, Analyzed *a)
+{
+   a->ptr = (char *)t->data; a->ndims = 0;
+   size_t nelem = 1;
+   for (int i = 0; i < t->ndims; i++) nelem *= t->size[i];
+   if (nelem == 0) { a->ndims = 1; a->size[0] = 0; a->strides[0] = 0; return; }
+   int n = 0;
+   for (int i = 0; i < t->ndims; i++) {
+      ptrdiff_t r = t->strides[i]; const size_t sz = t->size[i];
+      if (sz == 1 || r == 0) continue;
+      if (r < 0) { a->ptr += r * (ptrdiff_t)(sz - 1); r = -r; }
+      a->size[n] = sz; a->strides[n] = r; n++;
+   }
+   for (int i = 1; i < n; i++)                                          // insertion sort by stride
+      for (int j = i; j > 0 && a->strides[j] < a->strides[j - 1]; j--) {
+         std::swap(a->strides[j], a->strides[j - 1]); std::swap(a->size[j], a->size[j - 1]); }
+   int m = 0;
+   for (int i = 0; i < n; i++) {
+      if (m > 0 && a->strides[i] == a->strides[m - 1] * (ptrdiff_t)a->size[m - 1]) a->size[m - 1] *= a->size[i];
+      else { a->size[m] = a->size[i]; a->strides[m] = a->strides[i]; m++; }
+   }
+   a->ndims = m;
+}
+#define OCGPU_DEFINE_STEPS(OP, SOLID, PTYPE)                                                       \
+extern "C" int OcTensorGPU_##OP(const OcTensorView *tensor, PTYPE offset, PTYPE step)              \
+{                                                                                                  \
+   if (check_elemwise(tensor, "destination") != 0) return -1;                                      \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, tensor->dtype, #OP);                     \
+   if (f == nullptr) return -1;                                                                    \
+   if (set_device(tensor->device) != 0) return -1;                                                 \
+   Analyzed a; analyze1(tensor, &a);                                                               \
+   if (f(a.ndims, a.size, a.strides, a.ptr, offset, step, tensor->stream) != 0) return fail_solid(); \
+   return update(tensor);                                                                          \
+}
+OCGPU_DEFINE_STEPS(stepsInt64, steps_int64, solid_int64)
+OCGPU_DEFINE_STEPS(stepsDouble, steps_double, solid_double)
+OCGPU_DEFINE_STEPS(stepsCDouble, steps_cdouble, solid_cdouble)
 
 // ---------------------------------------------------------------------------------- copy / fill
 extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst)

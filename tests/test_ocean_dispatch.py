@@ -146,6 +146,30 @@ def test_scalar_forms_equal_tensor_forms(gpu):
 
 
 @pytest.mark.gpu
+def test_ranges_count_in_memory_order(gpu):
+    """OcTensorGPU_steps* reduce the tensor to its memory layout first, as the reference's dispatch does: a
+    matrix, its transpose and a view with a reversed dimension over the same bytes all receive the same values."""
+    from solid_b200 import Tensor
+    import ctypes as C
+    oc = _ocean.get(); oc.init()
+    t = Tensor.empty([12, 7], "float")
+    views = [t, t.T, t.as_strided([12, 7], [-4, 48], offset=44)]
+    want = (2.5 + 0.25 * np.arange(84)).astype(np.float32)
+    for v in views:
+        t.storage.zero_()
+        tv = oc.view(v, 0)
+        oc._check(oc.fn("stepsDouble")(C.byref(tv), C.c_double(2.5), C.c_double(0.25)), "stepsDouble")
+        assert np.array_equal(t.numpy().reshape(-1, order="F"), want)
+    k = Tensor.empty([5, 4], "int16")
+    kv = oc.view(k, 0)
+    oc._check(oc.fn("stepsInt64")(C.byref(kv), C.c_int64(-3), C.c_int64(2)), "stepsInt64")
+    assert np.array_equal(k.numpy().reshape(-1, order="F"), (-3 + 2 * np.arange(20)).astype(np.int16))
+    with pytest.raises(_ocean.OceanError, match="not supported for type"):
+        from solid_b200._lib import CDouble
+        oc._check(oc.fn("stepsCDouble")(C.byref(kv), CDouble(0, 0), CDouble(1, 0)), "stepsCDouble")
+
+
+@pytest.mark.gpu
 def test_stream_protocol_orders_producer_and_consumer(gpu):
     """The source is produced on one stream, the operation runs on the destination's stream: the
     dispatch must wait for the source's event, and record the destination's."""
