@@ -444,11 +444,13 @@ def run_ours(args):
             step(i)
         stop.record()
         barrier()
-        # keep the GPU under the same load until a few more samples exist
+        # keep the GPU under the same load until a few more samples exist.  The loop is bounded by the clock, so its
+        # trip count differs between ranks: it must not contain a collective (the kernel alone is the load).
         t_end = time.time() + 0.6
         while time.time() < t_end:
-            step()
-        torch.cuda.synchronize()
+            ops.axpy_sums(0.5, tx, ty, tz, sums)
+            torch.cuda.synchronize()
+        barrier()
     ms_total = start.elapsed_time(stop)
     kernel_ms = sum(a.elapsed_time(b) for a, b in zip(kstart, kstop)) / args.steps
     final = result.cpu().numpy().tolist()
