@@ -395,7 +395,9 @@ def run_ours(args):
     torch.cuda.set_device(local)
     device = torch.device("cuda", local)
     if world > 1:
-        dist.init_process_group("nccl", device_id=device)
+        import datetime
+        # a collective that cannot complete should end the run after minutes, not after the default ten
+        dist.init_process_group("nccl", device_id=device, timeout=datetime.timedelta(seconds=180))
     lib = _lib.get()
     lib.initialize()
     peak, peak_kind = measured_peak()
