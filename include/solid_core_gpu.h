@@ -148,6 +148,17 @@
 #define SOLID_GPU_ARGS_STEPS_INT64   SOLID_GPU_ARGS_STEPS_HEAD, solid_int64 offset, solid_int64 step, cudaStream_t stream
 #define SOLID_GPU_ARGS_STEPS_DOUBLE  SOLID_GPU_ARGS_STEPS_HEAD, solid_double offset, solid_double step, cudaStream_t stream
 #define SOLID_GPU_ARGS_STEPS_CDOUBLE SOLID_GPU_ARGS_STEPS_HEAD, solid_cdouble offset, solid_cdouble step, cudaStream_t stream
+#define SOLID_GPU_ARGS_INDEX2 \
+   int ndims, const size_t *size, solid_int64 **offsets, const ptrdiff_t *strides1, void *ptr1, \
+   const ptrdiff_t *strides2, void *ptr2, cudaStream_t stream
+#define SOLID_GPU_ARGS_FILL_INDEX \
+   int ndims, const size_t *size, solid_int64 **offsets, const ptrdiff_t *strides, void *ptr, \
+   const solid_scalar value, cudaStream_t stream
+#define SOLID_GPU_ARGS_ADD_IF_NEGATIVE \
+   int ndims, const size_t *size, const ptrdiff_t *strides, void *ptr, const solid_scalar value, cudaStream_t stream
+#define SOLID_GPU_ARGS_INDEX_TO_OFFSET \
+   int nstrides, solid_int64 *strides, ptrdiff_t strideReduce, size_t nelem, \
+   ptrdiff_t stride1, void *ptr1, ptrdiff_t stride2, void *ptr2, cudaStream_t stream
 #define SOLID_GPU_ARGS_COPY \
    int ndims1, const size_t *size1, const ptrdiff_t *strides1, void *ptr1, \
    int ndims2, const size_t *size2, const ptrdiff_t *strides2, void *ptr2, \
@@ -209,6 +220,25 @@ SOLID_GPU_DECLARE_(steps_double, all)
 #undef SOLID_GPU_ARGS_CURRENT_
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_STEPS_CDOUBLE
 SOLID_GPU_DECLARE_(steps_cdouble, complex)
+#undef SOLID_GPU_ARGS_CURRENT_
+
+/* Indexed access -- solid_core_gpu.src:72-99, template_index.cu:30-185.  `offsets` is a HOST array of ndims     */
+/* pointers; entry d is NULL (dimension d of the indexed tensor ptr1 is addressed by strides1[d]) or points to    */
+/* size[d] int64 BYTE offsets in DEVICE memory.  get: ptr2 = ptr1[index]; set: ptr1[index] = ptr2; fill:          */
+/* ptr[index] = value.  add_if_negative wraps negative indices (x < 0: x += value) in place; index_to_offset      */
+/* turns nelem index tuples (component i at ptr1 + e*stride1 + i*strideReduce) into int64 offsets sum strides[i]*index. */
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_INDEX2
+SOLID_GPU_DECLARE_(get_index, all)
+SOLID_GPU_DECLARE_(set_index, all)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_FILL_INDEX
+SOLID_GPU_DECLARE_(fill_index, all)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_ADD_IF_NEGATIVE
+SOLID_GPU_DECLARE_(add_if_negative, sint)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_INDEX_TO_OFFSET
+SOLID_GPU_DECLARE_(index_to_offset, integer)
 #undef SOLID_GPU_ARGS_CURRENT_
 
 /* strides2 == NULL and ptr2 == NULL: in place */

@@ -1,0 +1,172 @@
+// Indexed access: solid_gpu_{get,set,fill}_index_<T>, solid_gpu_add_if_negative_<T>, solid_gpu_index_to_offset_<T>.
+// Replaces solid/src/core/gpu/template_index.cu:30-185 with the kernel generators of
+// solid/include/solid/core/gpu/index1.h and index2.h.
+//
+// get/set/fill move whole elements, so there is one kernel per element LAYOUT (component size x component count:
+// complex elements are only aligned to their components), not per type.  A dimension either has a table of
+// int64 BYTE offsets in device memory (offsets[d] != NULL: element i of that dimension lies offsets[d][i] bytes
+// into the indexed tensor) or is addressed by its stride.  Positions are decomposed with 32-bit divisions
+// whenever they fit; four elements per thread are in flight, their accesses a block apart.
+#include "solid_core_gpu.h"
+#include "dtypes.cuh"
+#include "layout.h"
+#include "elemwise.cuh"
+
+namespace sd {
+
+struct IndexParams {
+   int            ndims;
+   uint64_t       nelem;
+   int64_t        size[MAXD];
+   const int64_t *offsets[MAXD];      // device pointers, or null
+   int64_t        stride1[MAXD], stride2[MAXD];
+   char          *ptr1, *ptr2;        // indexed tensor; dense-strided tensor (unused by fill)
+};
+
+template <int CS> struct raw_comp;
+template <> struct raw_comp<1> { using type = uint8_t; };
+template <> struct raw_comp<2> { using type = uint16_t; };
+template <> struct raw_comp<4> { using type = uint32_t; };
+template <> struct raw_comp<8> { using type = uint64_t; };
+template <int CS, int NC> struct RawElem { typename raw_comp<CS>::type c[NC]; };
+
+constexpr int IX_THREADS = 256, IX_U = 4;
+enum { IX_GET = 0, IX_SET = 1, IX_FILL = 2 };
+
+template <int CS, int NC, int MODE>
+__global__ void __launch_bounds__(IX_THREADS) index_kernel(const IndexParams p, const RawElem<CS, NC> value)
+{
+   using C = typename raw_comp<CS>::type;
+   const uint64_t base = (uint64_t)blockIdx.x * (IX_THREADS * IX_U) + threadIdx.x;
+   int64_t o1[IX_U], o2[IX_U]; bool ok[IX_U];
+#pragma unroll
+   for (int u = 0; u < IX_U; u++) {
+      uint64_t r = base + (uint64_t)u * IX_THREADS;
+      ok[u] = r < p.nelem;
+      o1[u] = 0; o2[u] = 0;
+      if (ok[u]) {
+         for (int d = 0; d < p.ndims; d++) {
+            const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
+            const int64_t *tab = p.offsets[d];
+            o1[u] += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
+            if (MODE != IX_FILL) o2[u] += (int64_t)c * p.stride2[d];
+         }
+      }
+   }
+   RawElem<CS, NC> e[IX_U];
+   if (MODE == IX_FILL) {
+#pragma unroll
+      for (int u = 0; u < IX_U; u++) e[u] = value;
+   } else {
+#pragma unroll
+      for (int u = 0; u < IX_U; u++) if (ok[u]) {
+         const C *q = reinterpret_cast<const C *>(MODE == IX_GET ? p.ptr1 + o1[u] : p.ptr2 + o2[u]);
+#pragma unroll
+         for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
+      }
+   }
+#pragma unroll
+   for (int u = 0; u < IX_U; u++) if (ok[u]) {
+      C *q = reinterpret_cast<C *>(MODE == IX_GET ? p.ptr2 + o2[u] : p.ptr1 + o1[u]);
+#pragma unroll
+      for (int k = 0; k < NC; k++) q[k] = e[u].c[k];
+   }
+}
+
+template <int CS, int NC, int MODE>
+int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptrdiff_t *strides1, void *ptr1,
+                 const ptrdiff_t *strides2, void *ptr2, const solid_scalar *value, cudaStream_t stream)
+{
+   if (ndims < 0 || ndims > MAXD) SD_ERROR("Number of dimensions (%d) exceeds the maximum of %d", ndims, MAXD);
+   IndexParams p; memset(&p, 0, sizeof(p));
+   p.ndims = ndims; p.nelem = 1; p.ptr1 = (char *)ptr1; p.ptr2 = (char *)ptr2;
+   for (int d = 0; d < ndims; d++) {
+      p.size[d] = (int64_t)size[d]; p.nelem *= (uint64_t)size[d];
+      p.offsets[d] = offsets ? offsets[d] : nullptr;
+      p.stride1[d] = strides1 ? strides1[d] : 0;
+      p.stride2[d] = (MODE != IX_FILL && strides2) ? strides2[d] : 0;
+   }
+   if (p.nelem == 0) return 0;
+   if (!aligned_to(ptr1, CS) || (MODE != IX_FILL && !aligned_to(ptr2, CS))) SD_ERROR("Tensor data must be aligned to the element size");
+   RawElem<CS, NC> v; memset(&v, 0, sizeof(v));
+   if (value) memcpy(&v, value, sizeof(v));
+   const uint64_t blocks = (p.nelem + IX_THREADS * IX_U - 1) / (IX_THREADS * IX_U);
+   if (blocks > 0x7FFFFFFFull) SD_ERROR("Indexed tensor too large for one launch");
+   index_kernel<CS, NC, MODE><<<(unsigned)blocks, IX_THREADS, 0, stream>>>(p, v);
+   SD_LAUNCH_CHECK();
+   return 0;
+}
+
+// element layouts of the fifteen types: component bytes, component count
+template <class T> struct elem_layout { static constexpr int CS = sizeof(T), NC = 1; };
+template <class E> struct elem_layout<Cplx<E>> { static constexpr int CS = sizeof(E), NC = 2; };
+
+// ---- add_if_negative: x < 0 ? x + value : x, in place (signed integers; used to wrap negative indices)
+template <class T> struct AddIfNegativeApply {
+   static constexpr int NIN = 1;
+   using in1_t = T; using in2_t = Nothing; using out_t = T;
+   T v;
+   SD_D T operator()(T x, Nothing) const { return x < 0 ? (T)(x + v) : x; }
+};
+
+// ---- index_to_offset: out[e] = sum_i strides[i] * index[e][i]
+struct OffsetParams { int nstrides; int64_t strides[MAXD]; int64_t stride_reduce, stride1, stride2; uint64_t nelem; const char *src; char *dst; };
+template <class T>
+__global__ void __launch_bounds__(256) index_to_offset_kernel(const OffsetParams p)
+{
+   const uint64_t e = (uint64_t)blockIdx.x * 256 + threadIdx.x;
+   if (e >= p.nelem) return;
+   const char *q = p.src + (int64_t)e * p.stride1;
+   int64_t s = 0;
+   for (int i = 0; i < p.nstrides; i++) s += p.strides[i] * (int64_t)ld_one<T>(q + i * p.stride_reduce);
+   *reinterpret_cast<int64_t *>(p.dst + (int64_t)e * p.stride2) = s;
+}
+
+} // namespace sd
+
+#define SD_IX_TYPE(TYPE) sd::ctype_of_##TYPE
+namespace sd {
+using ctype_of_bool = Bool; using ctype_of_uint8 = uint8_t; using ctype_of_uint16 = uint16_t; using ctype_of_uint32 = uint32_t;
+using ctype_of_uint64 = uint64_t; using ctype_of_int8 = int8_t; using ctype_of_int16 = int16_t; using ctype_of_int32 = int32_t;
+using ctype_of_int64 = int64_t; using ctype_of_half = Half; using ctype_of_float = float; using ctype_of_double = double;
+using ctype_of_chalf = CHalf; using ctype_of_cfloat = CFloat; using ctype_of_cdouble = CDouble;
+}
+
+#define SD_DEFINE_INDEX(U, TYPE)                                                                                      \
+   extern "C" int solid_gpu_get_index_##TYPE(SOLID_GPU_ARGS_INDEX2)                                                   \
+   {  using L = sd::elem_layout<SD_IX_TYPE(TYPE)>;                                                                    \
+      return sd::index_launch<L::CS, L::NC, sd::IX_GET>(ndims, size, offsets, strides1, ptr1, strides2, ptr2, nullptr, stream); } \
+   extern "C" int solid_gpu_set_index_##TYPE(SOLID_GPU_ARGS_INDEX2)                                                   \
+   {  using L = sd::elem_layout<SD_IX_TYPE(TYPE)>;                                                                    \
+      return sd::index_launch<L::CS, L::NC, sd::IX_SET>(ndims, size, offsets, strides1, ptr1, strides2, ptr2, nullptr, stream); } \
+   extern "C" int solid_gpu_fill_index_##TYPE(SOLID_GPU_ARGS_FILL_INDEX)                                              \
+   {  using L = sd::elem_layout<SD_IX_TYPE(TYPE)>;                                                                    \
+      return sd::index_launch<L::CS, L::NC, sd::IX_FILL>(ndims, size, offsets, strides, ptr, nullptr, nullptr, &value, stream); }
+SOLID_TYPES_all(SD_DEFINE_INDEX, u)
+
+#define SD_DEFINE_ADD_IF_NEGATIVE(U, TYPE)                                                                            \
+   extern "C" int solid_gpu_add_if_negative_##TYPE(SOLID_GPU_ARGS_ADD_IF_NEGATIVE)                                    \
+   {  using T = SD_IX_TYPE(TYPE);                                                                                     \
+      const ptrdiff_t *st[2] = { strides, strides }; void *pt[2] = { ptr, ptr };                                      \
+      sd::Layout<2> L;                                                                                                \
+      if (sd::make_layout<2>(L, ndims, size, st, pt, 1) != 0) return -1;                                              \
+      sd::AddIfNegativeApply<T> ap; memcpy(&ap.v, &value, sizeof(T));                                                 \
+      return sd::ew_launch(ap, L, stream); }
+SOLID_TYPES_sint(SD_DEFINE_ADD_IF_NEGATIVE, u)
+
+#define SD_DEFINE_INDEX_TO_OFFSET(U, TYPE)                                                                            \
+   extern "C" int solid_gpu_index_to_offset_##TYPE(SOLID_GPU_ARGS_INDEX_TO_OFFSET)                                    \
+   {  using T = SD_IX_TYPE(TYPE);                                                                                     \
+      if (nstrides < 0 || nstrides > sd::MAXD) SD_ERROR("Number of strides (%d) exceeds the maximum of %d", nstrides, sd::MAXD); \
+      if (nelem == 0) return 0;                                                                                       \
+      if (!sd::aligned_to(ptr1, sizeof(T)) || !sd::aligned_to(ptr2, 8)) SD_ERROR("Tensor data must be aligned to the element size"); \
+      sd::OffsetParams p; memset(&p, 0, sizeof(p));                                                                   \
+      p.nstrides = nstrides; for (int i = 0; i < nstrides; i++) p.strides[i] = strides[i];                            \
+      p.stride_reduce = strideReduce; p.stride1 = stride1; p.stride2 = stride2; p.nelem = nelem;                      \
+      p.src = (const char *)ptr1; p.dst = (char *)ptr2;                                                               \
+      const uint64_t blocks = ((uint64_t)nelem + 255) / 256;                                                          \
+      if (blocks > 0x7FFFFFFFull) SD_ERROR("index_to_offset: too many elements for one launch");                      \
+      sd::index_to_offset_kernel<T><<<(unsigned)blocks, 256, 0, stream>>>(p);                                         \
+      SD_LAUNCH_CHECK();                                                                                              \
+      return 0; }
+SOLID_TYPES_integer(SD_DEFINE_INDEX_TO_OFFSET, u)

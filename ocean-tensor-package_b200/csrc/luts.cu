@@ -10,6 +10,8 @@
 #define SD_LUT_all_nouint(P)    { P##bool, Z, Z, Z, Z,                                P##int8, P##int16, P##int32, P##int64, P##half, P##float, P##double, P##chalf, P##cfloat, P##cdouble }
 #define SD_LUT_all_nocomplex(P) { P##bool, P##uint8, P##uint16, P##uint32, P##uint64, P##int8, P##int16, P##int32, P##int64, P##half, P##float, P##double, Z, Z, Z }
 #define SD_LUT_integer_bool(P)  { P##bool, P##uint8, P##uint16, P##uint32, P##uint64, P##int8, P##int16, P##int32, P##int64, Z, Z, Z, Z, Z, Z }
+#define SD_LUT_sint(P)          { Z, Z, Z, Z, Z, P##int8, P##int16, P##int32, P##int64, Z, Z, Z, Z, Z, Z }
+#define SD_LUT_integer(P)       { Z, P##uint8, P##uint16, P##uint32, P##uint64, P##int8, P##int16, P##int32, P##int64, Z, Z, Z, Z, Z, Z }
 #define SD_LUT_bool(P)          { P##bool, Z, Z, Z, Z, Z, Z, Z, Z, Z, Z, Z, Z, Z, Z }
 #define SD_LUT_float(P)         { Z, Z, Z, Z, Z, Z, Z, Z, Z, P##half, P##float, P##double, P##chalf, P##cfloat, P##cdouble }
 #define SD_LUT_real(P)          { Z, Z, Z, Z, Z, Z, Z, Z, Z, P##half, P##float, P##double, Z, Z, Z }
@@ -26,6 +28,11 @@ SOLID_GPU_SCALAR_OPS(SD_DEFINE_LUT)
 SD_DEFINE_LUT(steps_int64, all)
 SD_DEFINE_LUT(steps_double, all)
 SD_DEFINE_LUT(steps_cdouble, complex)
+SD_DEFINE_LUT(get_index, all)
+SD_DEFINE_LUT(set_index, all)
+SD_DEFINE_LUT(fill_index, all)
+SD_DEFINE_LUT(add_if_negative, sint)
+SD_DEFINE_LUT(index_to_offset, integer)
 SOLID_GPU_REDUCE_BOOL_OPS(SD_DEFINE_LUT)
 SOLID_GPU_REDUCE_BOUND1_OPS(SD_DEFINE_LUT)
 SOLID_GPU_REDUCE_BOUND2_OPS(SD_DEFINE_LUT)

@@ -60,6 +60,10 @@ def _strides(seq):
     return (C.c_ssize_t * max(len(seq), 1))(*seq)
 
 
+def _pointers(seq):
+    return (C.c_void_p * max(len(seq), 1))(*[C.c_void_p(p) if p else None for p in seq])
+
+
 class CDouble(C.Structure):
     """solid_cdouble, passed by value to the steps_cdouble functions."""
     _fields_ = [("real", C.c_double), ("imag", C.c_double)]
@@ -145,6 +149,31 @@ class SolidGPU:
             args = (CDouble(complex(offset).real, complex(offset).imag), CDouble(complex(step).real, complex(step).imag))
         self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), *args, C.c_void_p(stream)),
                     "steps_%s_%s" % (kind, dtype))
+
+    # -- indexed access ----------------------------------------------------------------
+    def index2(self, name, dtype, size, offsets, strides1, ptr1, strides2, ptr2, stream=0):
+        """name 'get_index' (ptr2 = ptr1[index]) or 'set_index' (ptr1[index] = ptr2); offsets: per dimension a
+        device address of int64 byte offsets, or None where the dimension is addressed by strides1."""
+        f = self.fn("solid_gpu_%s_%s" % (name, dtype))
+        self._check(f(C.c_int(len(size)), _sizes(size), _pointers(offsets), _strides(strides1), C.c_void_p(ptr1),
+                      _strides(strides2), C.c_void_p(ptr2), C.c_void_p(stream)), "%s_%s" % (name, dtype))
+
+    def fill_index(self, dtype, size, offsets, strides, ptr, value: bytes, stream=0):
+        f = self.fn("solid_gpu_fill_index_%s" % dtype)
+        self._check(f(C.c_int(len(size)), _sizes(size), _pointers(offsets), _strides(strides), C.c_void_p(ptr),
+                      scalar_from_bytes(value), C.c_void_p(stream)), "fill_index_%s" % dtype)
+
+    def add_if_negative(self, dtype, size, strides, ptr, value: bytes, stream=0):
+        f = self.fn("solid_gpu_add_if_negative_%s" % dtype)
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), scalar_from_bytes(value),
+                      C.c_void_p(stream)), "add_if_negative_%s" % dtype)
+
+    def index_to_offset(self, dtype, strides, stride_reduce, nelem, stride1, ptr1, stride2, ptr2, stream=0):
+        f = self.fn("solid_gpu_index_to_offset_%s" % dtype)
+        arr = (C.c_int64 * max(len(strides), 1))(*strides)
+        self._check(f(C.c_int(len(strides)), arr, C.c_ssize_t(stride_reduce), C.c_size_t(nelem), C.c_ssize_t(stride1),
+                      C.c_void_p(ptr1), C.c_ssize_t(stride2), C.c_void_p(ptr2), C.c_void_p(stream)),
+                    "index_to_offset_%s" % dtype)
 
     def axpy(self, dtype, size, a: bytes, strides1, ptr1, strides2, ptr2, strides3, ptr3, stream=0):
         f = self.fn("solid_gpu_axpy_%s" % dtype)

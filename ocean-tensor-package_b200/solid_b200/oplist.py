@@ -22,6 +22,8 @@ BINARY_OPS = {
     "bitshift_left": "integer_bool", "bitshift_right": "integer_bool", "power": "all",
 }
 COMPARE_OPS = ["lt", "le", "ge", "gt", "eq", "ne"]
+INDEX_OPS = {"get_index": "all", "set_index": "all", "fill_index": "all", "add_if_negative": "sint",
+             "index_to_offset": "integer"}
 STEPS_OPS = {"steps_int64": "all", "steps_double": "all", "steps_cdouble": "complex"}
 # second operand passed by value (solid_gpu_<op>_scalar_<type>)
 SCALAR_OPS = {"add": "all", "subtract": "all", "multiply": "all",

@@ -103,6 +103,28 @@ class SolidCPU:
             args = (CDouble(complex(offset).real, complex(offset).imag), CDouble(complex(step).real, complex(step).imag))
         self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), *args), "steps")
 
+    # indexed access (solid/src/core/cpu/template_index.c): offsets are host addresses here
+    def index2(self, name, dtype, size, offsets, strides1, ptr1, strides2, ptr2):
+        ptrs = (C.c_void_p * max(len(offsets), 1))(*[C.c_void_p(p) if p else None for p in offsets])
+        self._check(self.fn("solid_cpu_%s_%s" % (name, dtype))(
+            C.c_int(len(size)), _sizes(size), ptrs, _strides(strides1), C.c_void_p(ptr1),
+            _strides(strides2), C.c_void_p(ptr2)), name)
+
+    def fill_index(self, dtype, size, offsets, strides, ptr, value: bytes):
+        ptrs = (C.c_void_p * max(len(offsets), 1))(*[C.c_void_p(p) if p else None for p in offsets])
+        self._check(self.fn("solid_cpu_fill_index_%s" % dtype)(
+            C.c_int(len(size)), _sizes(size), ptrs, _strides(strides), C.c_void_p(ptr), _scalar(value)), "fill_index")
+
+    def add_if_negative(self, dtype, size, strides, ptr, value: bytes):
+        self._check(self.fn("solid_cpu_add_if_negative_%s" % dtype)(
+            C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), _scalar(value)), "add_if_negative")
+
+    def index_to_offset(self, dtype, strides, stride_reduce, nelem, stride1, ptr1, stride2, ptr2):
+        arr = (C.c_int64 * max(len(strides), 1))(*strides)
+        self._check(self.fn("solid_cpu_index_to_offset_%s" % dtype)(
+            C.c_int(len(strides)), arr, C.c_ssize_t(stride_reduce), C.c_size_t(nelem), C.c_ssize_t(stride1),
+            C.c_void_p(ptr1), C.c_ssize_t(stride2), C.c_void_p(ptr2)), "index_to_offset")
+
     def byteswap(self, dtype, size, strides, ptr):
         self._check(self.fn("solid_cpu_byteswap_%s" % dtype)(
             C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr)), "byteswap")
