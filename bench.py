@@ -317,7 +317,25 @@ def ops_table(peak: float, with_cpu: bool, only=None, iters_scale: float = 1.0):
         hH = np.empty(m * m, dtype=np.uint16)
         add_row("C2", "copy f64 (offset 3 B, byteswapped) -> f16 4096^2", 10 * m * m, lambda: ops.copy(tU, tH),
                 (lambda: cpu.copy("double", "half", [m * m], [8], raw.ctypes.data + 3, [m * m], [2], hH.ctypes.data, variant="byteswap_copy")) if cpu else None)
-        del tA, tB, tC, tU, tH
+        # gather through offset tables (get_index): rows (the dense dimension) or columns of a column-major matrix
+        gm, gn = 8192, 4096
+        G = rng.normal(size=(gm, gn)).astype(np.float32)
+        hG = np.asfortranarray(G)
+        tG, tS = dev(hG), Tensor.empty([gm, gn], "float")
+        hS = np.empty((gm, gn), dtype=np.float32, order="F")
+        row_tab = (rng.permutation(gm).astype(np.int64) * 4); col_tab = (rng.permutation(gn).astype(np.int64) * 4 * gm)
+        d_rows = torch.from_numpy(row_tab).cuda(); d_cols = torch.from_numpy(col_tab).cuda()
+        add_row("C2", "get_index rows A[perm, :] f32 8192x4096 (4-byte gathers)", 8 * gm * gn,
+                lambda: lib.index2("get_index", "float", [gm, gn], [d_rows.data_ptr(), None], [0, 4 * gm], tG.ptr,
+                                   [4, 4 * gm], tS.ptr, cur), iters=10,
+                cpu_fn=(lambda: cpu.index2("get_index", "float", [gm, gn], [row_tab.ctypes.data, None], [0, 4 * gm], hG.ctypes.data,
+                                           [4, 4 * gm], hS.ctypes.data)) if cpu else None)
+        add_row("C2", "get_index columns A[:, perm] f32 8192x4096 (32 KB runs)", 8 * gm * gn,
+                lambda: lib.index2("get_index", "float", [gm, gn], [None, d_cols.data_ptr()], [4, 0], tG.ptr,
+                                   [4, 4 * gm], tS.ptr, cur), iters=10,
+                cpu_fn=(lambda: cpu.index2("get_index", "float", [gm, gn], [None, col_tab.ctypes.data], [4, 0], hG.ctypes.data,
+                                           [4, 4 * gm], hS.ctypes.data)) if cpu else None)
+        del tA, tB, tC, tU, tH, tG, tS
 
     # ---- C3: axis reductions on 8192^2 (column-major: axis 0 is the dense one), global any/all/nnz on bool
     if only in (None, "C3"):

@@ -33,19 +33,29 @@ template <int CS, int NC> struct RawElem { typename raw_comp<CS>::type c[NC]; };
 constexpr int IX_THREADS = 256, IX_U = 4;
 enum { IX_GET = 0, IX_SET = 1, IX_FILL = 2 };
 
-template <int CS, int NC, int MODE>
+// A thread moves IX_U groups of V consecutive positions of dimension 0.  V > 1 is used when the dense-strided
+// tensor (ptr2) is contiguous and 16-byte aligned along dimension 0: its side is then one 16-byte access per
+// group, and the position is decomposed once per group.  The indexed side (ptr1) is always accessed element by
+// element, because the alignment of table entries (device data) is not known when the kernel is chosen.
+template <int CS, int NC, int MODE, int V>
 __global__ void __launch_bounds__(IX_THREADS) index_kernel(const IndexParams p, const RawElem<CS, NC> value)
 {
    using C = typename raw_comp<CS>::type;
+   using E = RawElem<CS, NC>;
+   const uint64_t ngroups = p.nelem / V;
    const uint64_t base = (uint64_t)blockIdx.x * (IX_THREADS * IX_U) + threadIdx.x;
-   int64_t o1[IX_U], o2[IX_U]; bool ok[IX_U];
+   const uint64_t size0 = (uint64_t)p.size[0] / V;
+   const int64_t *tab0 = p.ndims > 0 ? p.offsets[0] : nullptr;
+   int64_t o1[IX_U], o2[IX_U]; uint64_t c0[IX_U]; bool ok[IX_U];
 #pragma unroll
    for (int u = 0; u < IX_U; u++) {
       uint64_t r = base + (uint64_t)u * IX_THREADS;
-      ok[u] = r < p.nelem;
-      o1[u] = 0; o2[u] = 0;
-      if (ok[u]) {
-         for (int d = 0; d < p.ndims; d++) {
+      ok[u] = r < ngroups;
+      o1[u] = 0; o2[u] = 0; c0[u] = 0;
+      if (ok[u] && p.ndims > 0) {
+         {  const uint64_t q = udiv64(r, size0); c0[u] = (r - q * size0) * V; r = q; }
+         if (MODE != IX_FILL) o2[u] = (int64_t)c0[u] * p.stride2[0];
+         for (int d = 1; d < p.ndims; d++) {
             const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
             const int64_t *tab = p.offsets[d];
             o1[u] += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
@@ -53,23 +63,59 @@ __global__ void __launch_bounds__(IX_THREADS) index_kernel(const IndexParams p, 
          }
       }
    }
-   RawElem<CS, NC> e[IX_U];
+   // offsets of the V positions along dimension 0 on the indexed side
+   int64_t d1[IX_U][V];
+#pragma unroll
+   for (int u = 0; u < IX_U; u++) {
+#pragma unroll
+      for (int j = 0; j < V; j++)
+         d1[u][j] = !ok[u] ? 0 : (tab0 ? __ldg(tab0 + c0[u] + j) : (int64_t)(c0[u] + j) * p.stride1[0]);
+   }
+   Vec<E, V> e[IX_U];
    if (MODE == IX_FILL) {
 #pragma unroll
-      for (int u = 0; u < IX_U; u++) e[u] = value;
+      for (int u = 0; u < IX_U; u++) {
+#pragma unroll
+         for (int j = 0; j < V; j++) e[u].v[j] = value;
+      }
+   } else if (MODE == IX_GET) {
+#pragma unroll
+      for (int u = 0; u < IX_U; u++) if (ok[u]) {
+#pragma unroll
+         for (int j = 0; j < V; j++) {
+            const C *q = reinterpret_cast<const C *>(p.ptr1 + o1[u] + d1[u][j]);
+#pragma unroll
+            for (int k = 0; k < NC; k++) e[u].v[j].c[k] = q[k];
+         }
+      }
    } else {
 #pragma unroll
       for (int u = 0; u < IX_U; u++) if (ok[u]) {
-         const C *q = reinterpret_cast<const C *>(MODE == IX_GET ? p.ptr1 + o1[u] : p.ptr2 + o2[u]);
+         if (V > 1) e[u] = ld_vec<E, V>(p.ptr2 + o2[u]);
+         else {
+            const C *q = reinterpret_cast<const C *>(p.ptr2 + o2[u]);
 #pragma unroll
-         for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
+            for (int k = 0; k < NC; k++) e[u].v[0].c[k] = q[k];
+         }
       }
    }
 #pragma unroll
    for (int u = 0; u < IX_U; u++) if (ok[u]) {
-      C *q = reinterpret_cast<C *>(MODE == IX_GET ? p.ptr2 + o2[u] : p.ptr1 + o1[u]);
+      if (MODE == IX_GET) {
+         if (V > 1) st_vec<E, V>(p.ptr2 + o2[u], e[u]);
+         else {
+            C *q = reinterpret_cast<C *>(p.ptr2 + o2[u]);
 #pragma unroll
-      for (int k = 0; k < NC; k++) q[k] = e[u].c[k];
+            for (int k = 0; k < NC; k++) q[k] = e[u].v[0].c[k];
+         }
+      } else {
+#pragma unroll
+         for (int j = 0; j < V; j++) {
+            C *q = reinterpret_cast<C *>(p.ptr1 + o1[u] + d1[u][j]);
+#pragma unroll
+            for (int k = 0; k < NC; k++) q[k] = e[u].v[j].c[k];
+         }
+      }
    }
 }
 
@@ -77,6 +123,8 @@ template <int CS, int NC, int MODE>
 int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptrdiff_t *strides1, void *ptr1,
                  const ptrdiff_t *strides2, void *ptr2, const solid_scalar *value, cudaStream_t stream)
 {
+   constexpr int ES = CS * NC;
+   constexpr int V = 16 / ES > 1 ? 16 / ES : 1;
    if (ndims < 0 || ndims > MAXD) SD_ERROR("Number of dimensions (%d) exceeds the maximum of %d", ndims, MAXD);
    IndexParams p; memset(&p, 0, sizeof(p));
    p.ndims = ndims; p.nelem = 1; p.ptr1 = (char *)ptr1; p.ptr2 = (char *)ptr2;
@@ -90,9 +138,17 @@ int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptr
    if (!aligned_to(ptr1, CS) || (MODE != IX_FILL && !aligned_to(ptr2, CS))) SD_ERROR("Tensor data must be aligned to the element size");
    RawElem<CS, NC> v; memset(&v, 0, sizeof(v));
    if (value) memcpy(&v, value, sizeof(v));
-   const uint64_t blocks = (p.nelem + IX_THREADS * IX_U - 1) / (IX_THREADS * IX_U);
+   // groups of V along dimension 0: the dense-strided side must be contiguous there and 16-byte aligned everywhere
+   bool vec = V > 1 && ndims > 0 && size[0] % V == 0;
+   if (vec && MODE != IX_FILL) {
+      vec = p.stride2[0] == ES && aligned_to(ptr2, 16);
+      for (int d = 1; d < ndims && vec; d++) if (p.stride2[d] % 16 != 0) vec = false;
+   }
+   const uint64_t groups = p.nelem / (vec ? V : 1);
+   const uint64_t blocks = (groups + IX_THREADS * IX_U - 1) / (IX_THREADS * IX_U);
    if (blocks > 0x7FFFFFFFull) SD_ERROR("Indexed tensor too large for one launch");
-   index_kernel<CS, NC, MODE><<<(unsigned)blocks, IX_THREADS, 0, stream>>>(p, v);
+   if (vec) index_kernel<CS, NC, MODE, V><<<(unsigned)blocks, IX_THREADS, 0, stream>>>(p, v);
+   else     index_kernel<CS, NC, MODE, 1><<<(unsigned)blocks, IX_THREADS, 0, stream>>>(p, v);
    SD_LAUNCH_CHECK();
    return 0;
 }
