@@ -257,6 +257,29 @@ OCGPU_DEFINE_STEPS(stepsInt64, steps_int64, solid_int64)
 OCGPU_DEFINE_STEPS(stepsDouble, steps_double, solid_double)
 OCGPU_DEFINE_STEPS(stepsCDouble, steps_cdouble, solid_cdouble)
 
+// Can kernels on device `reader` load memory of device `owner`?  Asked of the runtime once per pair; peer access is
+// switched on at that moment (another library in the process may have done so already, which is not an error).
+static bool peer_readable(int reader, int owner)
+{
+   static signed char known[64][64];                       // 0 not asked, 1 yes, -1 no
+   static std::mutex lock;
+   if (reader < 0 || reader >= 64 || owner < 0 || owner >= 64) return false;
+   std::lock_guard<std::mutex> guard(lock);
+   if (known[reader][owner] == 0) {
+      int can = 0, current = -1;
+      known[reader][owner] = -1;
+      if (cudaDeviceCanAccessPeer(&can, reader, owner) == cudaSuccess && can && cudaGetDevice(&current) == cudaSuccess) {
+         if (cudaSetDevice(reader) == cudaSuccess) {
+            cudaError_t st = cudaDeviceEnablePeerAccess(owner, 0);
+            if (st == cudaSuccess || st == cudaErrorPeerAccessAlreadyEnabled) known[reader][owner] = 1;
+            (void)cudaGetLastError();
+         }
+         cudaSetDevice(current);
+      } else (void)cudaGetLastError();
+   }
+   return known[reader][owner] > 0;
+}
+
 // ---------------------------------------------------------------------------------- copy / fill
 extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst)
 {
@@ -271,8 +294,26 @@ extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst
    if (src->device == dst->device) {
       if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, src->ndims, src->size, src->strides, src->data,
                             dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+   } else if (peer_readable(dst->device, src->device)) {
+      // other device, readable through a peer mapping (NVLink on the HGX boards): the converting copy kernel runs on
+      // the destination device and loads the source over the link with plain loads -- one pass, no temporaries on
+      // either side.  The two streams belong to different devices, so they are ordered by events made here: the
+      // kernel starts after the source stream's earlier work, and the source stream continues after the kernel.
+      cudaEvent_t before, after;
+      if (set_device(src->device) != 0) return -1;
+      if (cudaEventCreateWithFlags(&before, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
+      cudaEventRecord(before, src->stream);
+      if (set_device(dst->device) != 0) { cudaEventDestroy(before); return -1; }
+      cudaStreamWaitEvent(dst->stream, before, 0);
+      cudaEventDestroy(before);
+      if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, src->ndims, src->size, src->strides, src->data,
+                            dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+      if (cudaEventCreateWithFlags(&after, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
+      cudaEventRecord(after, dst->stream);
+      cudaStreamWaitEvent(src->stream, after, 0);
+      cudaEventDestroy(after);
    } else {
-      // other device: gather into a dense buffer of the source type on the source device, move it
+      // other device without peer access: gather into a dense buffer of the source type on the source device, move it
       // with one peer copy, convert on the destination (OcTensor_intrnlCopyDevices, tensor_itf.c:895-1041)
       const size_t bytes = n1 * (size_t)solid_gpu_type_size[src->dtype];
       void *tmp_src = nullptr, *tmp_dst = nullptr;

@@ -212,3 +212,15 @@ def test_copy_between_devices(gpu):
     ops.copy(src.slice(0, 99999, -1, -1), dst)               # reversed, converted, other device
     torch.cuda.synchronize(0); torch.cuda.synchronize(1)
     assert np.array_equal(dst.numpy(), x[::-1].astype(np.float64))
+    # a transposed matrix, the other way round, then back into a padded destination: repeated so that a
+    # missing ordering between the two devices' streams would show
+    m = np.random.default_rng(3).normal(size=(300, 200)).astype(np.float32)
+    on1 = Tensor.from_numpy(np.asfortranarray(m), device="cuda:1")
+    for _ in range(4):
+        on0 = Tensor.empty([200, 300], "double", device="cuda:0")
+        ops.copy(on1.T, on0)
+        back = Tensor.empty([300, 200], "float", device="cuda:1")
+        ops.copy(on0.T, back)
+        torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+        assert np.array_equal(on0.numpy(), m.T.astype(np.float64))
+        assert np.array_equal(back.numpy(), m)
