@@ -590,3 +590,80 @@ def mixed_multiply_add(ctype: str, dst: str, a, ta: str, b, tb: str, c, tc: str,
         ops.append(convert(t, ctype, byteswap(t, arr) if sw else arr))
     prod = binary("multiply", ctype, ops[0], ops[1])
     return convert(ctype, dst, binary("add", ctype, prod, ops[2]))
+
+
+# ----------------------------------------------------------------------------
+# ranges and indexed access
+# ----------------------------------------------------------------------------
+def steps(kind: str, dtype: str, n: int, offset, step) -> np.ndarray:
+    """Element i = offset + i * step cast to `dtype` (solid/src/core/cpu/template_steps.c:27-92), i = 0..n-1 in
+    the column-major order of the tensor.  kind 'int64': the position is a size_t, so the sum is formed in
+    unsigned 64-bit arithmetic and THEN cast to the work type (negative results reach floating-point tensors as
+    values near 2^64); kind 'double': product and sum in double; kind 'cdouble': both components (the real one
+    only for real element types).  In-range values only for the double -> integer casts."""
+    i = np.arange(n, dtype=np.uint64)
+    et = {"chalf": "half", "cfloat": "float", "cdouble": "double"}.get(dtype, dtype)
+
+    def cast_u64(u):
+        if et == "bool":
+            return (u & np.uint64(0xFF)).astype(np.uint8)
+        if et == "half":
+            return float_to_half(u.astype(np.float32))
+        return u.astype(NP[et])
+
+    def cast_double(d):
+        if et == "bool":
+            return (np.trunc(d).astype(np.int64) & 0xFF).astype(np.uint8)
+        return _convert_real("double", et, d)
+
+    with np.errstate(over="ignore"):
+        if kind == "int64":
+            u = np.uint64(int(offset) & 0xFFFFFFFFFFFFFFFF) + i * np.uint64(int(step) & 0xFFFFFFFFFFFFFFFF)
+            re, im = cast_u64(u), None
+        elif kind == "double":
+            re, im = cast_double(np.float64(offset) + i.astype(np.float64) * np.float64(step)), None
+        else:
+            o, s = complex(offset), complex(step)
+            re = cast_double(np.float64(o.real) + i.astype(np.float64) * np.float64(s.real))
+            im = cast_double(np.float64(o.imag) + i.astype(np.float64) * np.float64(s.imag))
+    if dtype not in ("chalf", "cfloat", "cdouble"):
+        return re
+    if im is None:
+        im = np.zeros(n, dtype=NP[et])
+    if dtype == "chalf":
+        out = np.zeros(n, dtype=NP["chalf"]); out["real"] = re; out["imag"] = im
+        return out
+    return _complex(re, im, NP[dtype])
+
+
+def index_offsets(size, tables, strides) -> np.ndarray:
+    """Byte offset of every selected element, column-major over `size`: dimension d contributes tables[d][i]
+    where it has a table and i * strides[d] otherwise (solid/include/solid/core/gpu/index2.h:288-305)."""
+    off = np.zeros(1, dtype=np.int64)
+    for d in range(len(size) - 1, -1, -1):
+        part = np.asarray(tables[d], dtype=np.int64) if tables[d] is not None else np.arange(size[d], dtype=np.int64) * strides[d]
+        off = (off[:, None] + part[None, :]).reshape(-1)
+    return off
+
+
+def get_index(src_bytes: np.ndarray, elemsize: int, size, tables, strides) -> np.ndarray:
+    """Selected elements of a byte buffer as an (n, elemsize) byte matrix, column-major selection order."""
+    off = index_offsets(size, tables, strides)
+    return src_bytes[off[:, None] + np.arange(elemsize)[None, :]]
+
+
+def set_index(dst_bytes: np.ndarray, elemsize: int, size, tables, strides, values: np.ndarray) -> None:
+    """Scatter an (n, elemsize) byte matrix; later elements win where positions repeat."""
+    off = index_offsets(size, tables, strides)
+    dst_bytes[off[:, None] + np.arange(elemsize)[None, :]] = values
+
+
+def add_if_negative(x: np.ndarray, value) -> np.ndarray:
+    with np.errstate(over="ignore"):
+        return np.where(x < 0, x + x.dtype.type(value), x).astype(x.dtype)
+
+
+def index_to_offset(index: np.ndarray, strides) -> np.ndarray:
+    """index[i, e] (component i of tuple e) -> sum_i strides[i] * index[i, e] as int64."""
+    with np.errstate(over="ignore"):
+        return (np.asarray(strides, dtype=np.int64)[:, None] * index.astype(np.int64)).sum(axis=0, dtype=np.int64)

@@ -167,3 +167,52 @@ def test_fused_sequences_match_reference_library(cpu):
     cpu.copy("double", "float", [n], [8], S.ctypes.data, [n], [4], Cf.ctypes.data)
     got = sn.mixed_multiply_add("double", "float", A, "double", Bs, "int32", r, "float", swapped=(False, True, False))
     assert np.array_equal(got, Cf)
+
+
+def test_ranges_and_indexed_access_match_reference_library(cpu):
+    """The numpy restatements of steps_*, get/set/fill_index, add_if_negative and index_to_offset against the
+    compiled reference (needs oracle/_ref)."""
+    rng = np.random.default_rng(5)
+    n = 300
+    for dtype in dt.NAMES:
+        es = dt.SIZE[dtype]
+        kinds = [("int64", 7, 3), ("int64", -5, 2), ("double", 0.25, 0.5), ("double", 100.0, -0.375)]
+        if dtype in dt.COMPLEX:
+            kinds.append(("cdouble", 1 - 2j, 0.5 + 0.25j))
+        for kind, off, step in kinds:
+            if kind == "double" and step < 0 and (dtype in dt.UINT or dtype == "bool"):
+                continue                                    # negative double -> unsigned: undefined in C, not restated
+            if kind == "int64" and off < 0 and dtype == "half":
+                pass                                        # 2^64-ish values: float_to_half saturates to inf the same way
+            buf = np.zeros(n * es, dtype=np.uint8)
+            cpu.steps(kind, dtype, [n], [es], buf.ctypes.data, off, step)
+            got = sn.steps(kind, dtype, n, off, step)
+            assert got.tobytes() == buf.tobytes(), (kind, dtype, off, step)
+        # gather / scatter / fill through a table on dimension 0 and a stride on dimension 1 (column-major 40 x 30)
+        src = rng.integers(0, 256, 40 * 30 * es).astype(np.uint8)
+        tab = (rng.permutation(40)[:17].astype(np.int64)) * es
+        sel = np.zeros(17 * 30 * es, dtype=np.uint8)
+        cpu.index2("get_index", dtype, [17, 30], [tab.ctypes.data, None], [0, 40 * es], src.ctypes.data, [es, 17 * es], sel.ctypes.data)
+        assert np.array_equal(sn.get_index(src, es, [17, 30], [tab, None], [0, 40 * es]).reshape(-1), sel), dtype
+        dst = src.copy(); want = src.copy()
+        vals = rng.integers(0, 256, 17 * 30 * es).astype(np.uint8)
+        cpu.index2("set_index", dtype, [17, 30], [tab.ctypes.data, None], [0, 40 * es], want.ctypes.data, [es, 17 * es], vals.ctypes.data)
+        sn.set_index(dst, es, [17, 30], [tab, None], [0, 40 * es], vals.reshape(-1, es))
+        assert np.array_equal(dst, want), dtype
+        value = rng.integers(0, 256, es).astype(np.uint8)
+        dst = src.copy(); want = src.copy()
+        cpu.fill_index(dtype, [17, 30], [tab.ctypes.data, None], [0, 40 * es], want.ctypes.data, value.tobytes())
+        sn.set_index(dst, es, [17, 30], [tab, None], [0, 40 * es], np.broadcast_to(value, (17 * 30, es)))
+        assert np.array_equal(dst, want), dtype
+    for dtype in dt.SINT:
+        x = rng.integers(-60, 60, 500).astype(dt.NUMPY[dtype])
+        want = x.copy()
+        cpu.add_if_negative(dtype, [500], [dt.SIZE[dtype]], want.ctypes.data, np.array([60], dtype=dt.NUMPY[dtype]).tobytes())
+        assert np.array_equal(sn.add_if_negative(x, 60), want), dtype
+    for dtype in dt.UINT + dt.SINT:
+        idx = np.asfortranarray(rng.integers(0, 100, (3, 200)).astype(dt.NUMPY[dtype]))
+        strides = [8, -640, 5120]
+        es = dt.SIZE[dtype]
+        out = np.zeros(200, dtype=np.int64)
+        cpu.index_to_offset(dtype, strides, es, 200, 3 * es, idx.ctypes.data, 8, out.ctypes.data)
+        assert np.array_equal(sn.index_to_offset(idx, strides), out), dtype
