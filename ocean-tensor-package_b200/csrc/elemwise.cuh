@@ -67,23 +67,10 @@ template <class A> struct ew_traits {
 // next to its per-element operator() (announced by  static constexpr bool VECTOR = true): it then sees the
 // whole vector of a thread-iteration and can take shortcuts that depend on all of its elements.
 // An apply object may also ask for a number of resident blocks per multiprocessor (static constexpr int MIN_BLOCKS).
-template <class A, class = void> struct ew_min_blocks { static constexpr int value = 1; };
+template <class A, class = void> struct ew_min_blocks { static constexpr int value = 0; };   // 0: no request
 template <class A> struct ew_min_blocks<A, std::enable_if_t<(A::MIN_BLOCKS > 0)>> { static constexpr int value = A::MIN_BLOCKS; };
 template <class A, class = void> struct has_vector_apply : std::false_type {};
 template <class A> struct has_vector_apply<A, std::enable_if_t<A::VECTOR>> : std::true_type {};
-
-template <class A, int N>
-SD_D Vec<typename A::out_t, N> ew_apply(const A &apply, const Vec<typename A::in1_t, N> &a, const Vec<typename A::in2_t, N> &b)
-{
-   if constexpr (has_vector_apply<A>::value && (N > 1)) {
-      return apply.template vec<N>(a, b);
-   } else {
-      Vec<typename A::out_t, N> o;
-#pragma unroll
-      for (int j = 0; j < N; j++) o.v[j] = apply(a.v[j], b.v[j]);
-      return o;
-   }
-}
 
 // Access to elements that do not start on a multiple of their size (only the copy
 // family accepts such tensors).  Loads fetch the aligned 32-bit words that cover
@@ -210,7 +197,12 @@ __global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig
       for (int u = 0; u < U; u++) {
          uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
          if (i < nvec) {
-            const Vec<out_t, VEC> o = ew_apply<A, VEC>(apply, a[u], b[u]);
+            Vec<out_t, VEC> o;
+            if constexpr (has_vector_apply<A>::value && (VEC > 1)) o = apply.template vec<VEC>(a[u], b[u]);
+            else {
+#pragma unroll
+               for (int j = 0; j < VEC; j++) o.v[j] = apply(a[u].v[j], b[u].v[j]);
+            }
             ew_store<out_t, VEC, UNAL>(po + i * (VEC * sizeof(out_t)), o, uo);
          }
       }
@@ -269,7 +261,12 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
       Vec<in1_t, VEC> a; Vec<in2_t, VEC> b;
       if constexpr (NIN >= 1) a = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + off[0], VEC > 1 && b1, u1);
       if constexpr (NIN >= 2) b = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + off[1], VEC > 1 && b2, u2);
-      const Vec<out_t, VEC> o = ew_apply<A, VEC>(apply, a, b);
+      Vec<out_t, VEC> o;
+      if constexpr (has_vector_apply<A>::value && (VEC > 1)) o = apply.template vec<VEC>(a, b);
+      else {
+#pragma unroll
+         for (int j = 0; j < VEC; j++) o.v[j] = apply(a.v[j], b.v[j]);
+      }
       ew_store<out_t, VEC, UNAL>(p.ptr[NIN] + off[NIN], o, uo);
    }
 }
