@@ -85,6 +85,18 @@
    X(bitshift_left, integer_bool) X(bitshift_right, integer_bool) \
    X(power, all)
 
+/* Unary functions with a domain, fused with the domain test that Ocean runs as a separate global reduction      */
+/* before them (OcTensor_sqrt and relatives, src/core/interface/tensor_itf.c:3822-3871: anyLTZero, anyLTNegOne,     */
+/* anyLTOne, anyGTOneAbs; OcTensor_reciprocal :3786-3810: anyEQZero).  No counterpart in the reference's Solid      */
+/* layer.  The result is that of the plain function; `outside` (device int, zeroed by the caller) is set to 1      */
+/* when an element fails the test the reference applies: x < 0 for sqrt/log/log2/log10, x < -1 for log1p, x < 1     */
+/* for arccosh, x < -1 or x > 1 for arcsin/arccos/arctanh, x == 0 for reciprocal (a NaN passes all of them, as in   */
+/* the reference's all_ge / all_gele reductions).  One pass over the data instead of two.  Real floating types.     */
+#define SOLID_GPU_CHECKED_OPS(X) \
+   X(sqrt_checked, real) X(log_checked, real) X(log2_checked, real) X(log10_checked, real) X(log1p_checked, real) \
+   X(arccosh_checked, real) X(arcsin_checked, real) X(arccos_checked, real) X(arctanh_checked, real) \
+   X(reciprocal_checked, real)
+
 /* Binary operations with the second operand a scalar passed BY VALUE: dst = op(src, value).      */
 /* No counterpart in the reference's Solid layer: Ocean's addScalar, subtractScalar, multiplyScalar */
 /* and bitwise{And,Or,Xor}Scalar build a 0-d device tensor from the scalar and call the tensor     */
@@ -136,6 +148,9 @@
 #define SOLID_GPU_ARGS_UNARY \
    int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, \
    const ptrdiff_t *strides2, void *ptr2, cudaStream_t stream
+#define SOLID_GPU_ARGS_UNARY_CHECKED \
+   int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, \
+   const ptrdiff_t *strides2, void *ptr2, int *outside, cudaStream_t stream
 #define SOLID_GPU_ARGS_BINARY \
    int ndims, const size_t *size, const ptrdiff_t *strides1, void *ptr1, \
    const ptrdiff_t *strides2, void *ptr2, const ptrdiff_t *strides3, void *ptr3, \
@@ -203,6 +218,10 @@ SOLID_GPU_DECLARE_(masked_fill, all)
 
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_UNARY
 SOLID_GPU_UNARY_OPS(SOLID_GPU_DECLARE_)
+#undef SOLID_GPU_ARGS_CURRENT_
+
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_UNARY_CHECKED
+SOLID_GPU_CHECKED_OPS(SOLID_GPU_DECLARE_)
 #undef SOLID_GPU_ARGS_CURRENT_
 
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_BINARY

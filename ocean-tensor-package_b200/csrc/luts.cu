@@ -23,6 +23,7 @@
 SOLID_GPU_FILL_OPS(SD_DEFINE_LUT)
 SD_DEFINE_LUT(masked_fill, all)
 SOLID_GPU_UNARY_OPS(SD_DEFINE_LUT)
+SOLID_GPU_CHECKED_OPS(SD_DEFINE_LUT)
 SOLID_GPU_BINARY_OPS(SD_DEFINE_LUT)
 SOLID_GPU_SCALAR_OPS(SD_DEFINE_LUT)
 SD_DEFINE_LUT(steps_int64, all)

@@ -150,6 +150,14 @@ class SolidGPU:
         self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr), *args, C.c_void_p(stream)),
                     "steps_%s_%s" % (kind, dtype))
 
+    def unary_checked(self, name, dtype, size, strides1, ptr1, strides2, ptr2, flag_ptr, stream=0):
+        """solid_gpu_<name>_checked_<dtype>: the unary function plus a device int flag set when an element lies
+        outside the function's real domain."""
+        f = self.fn("solid_gpu_%s_checked_%s" % (name, dtype))
+        st2 = _strides(strides2) if strides2 is not None else None
+        self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1), st2, C.c_void_p(ptr2),
+                      C.c_void_p(flag_ptr), C.c_void_p(stream)), "%s_checked_%s" % (name, dtype))
+
     # -- indexed access ----------------------------------------------------------------
     def index2(self, name, dtype, size, offsets, strides1, ptr1, strides2, ptr2, stream=0):
         """name 'get_index' (ptr2 = ptr1[index]) or 'set_index' (ptr1[index] = ptr2); offsets: per dimension a

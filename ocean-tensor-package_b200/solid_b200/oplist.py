@@ -22,6 +22,9 @@ BINARY_OPS = {
     "bitshift_left": "integer_bool", "bitshift_right": "integer_bool", "power": "all",
 }
 COMPARE_OPS = ["lt", "le", "ge", "gt", "eq", "ne"]
+# unary functions fused with their domain test: name -> (type group, reference test)
+CHECKED_OPS = {"sqrt": "real", "log": "real", "log2": "real", "log10": "real", "log1p": "real", "arccosh": "real",
+               "arcsin": "real", "arccos": "real", "arctanh": "real", "reciprocal": "real"}
 INDEX_OPS = {"get_index": "all", "set_index": "all", "fill_index": "all", "add_if_negative": "sint",
              "index_to_offset": "integer"}
 STEPS_OPS = {"steps_int64": "all", "steps_double": "all", "steps_cdouble": "complex"}

@@ -286,3 +286,82 @@ def test_scalar_operand_by_value_matches_broadcast_tensor(op, gpu, cpu):
                 got = dev.download(dd)
                 util.assert_same(util.gather(got, vo), util.gather(want, vo), dtype, 0,
                                  "%s_scalar_%s %s%s" % (op, dtype, name, " in place" if in_place else ""))
+
+
+@pytest.mark.parametrize("op", sorted(ol.CHECKED_OPS))
+def test_checked_unary_equals_function_plus_domain_reduction(op, gpu, cpu):
+    """solid_gpu_<op>_checked_<type> = the unary function (compared with the tolerance of that function) and the
+    domain test the reference runs as a separate global reduction: not all_ge(bound) / not all in [-1, 1] /
+    not all (nonzero), computed here with the reference's own reductions on the same data."""
+    dev = util.Device()
+    bounds = {"sqrt": ("all_ge", 0.0), "log": ("all_ge", 0.0), "log2": ("all_ge", 0.0), "log10": ("all_ge", 0.0),
+              "log1p": ("all_ge", -1.0), "arccosh": ("all_ge", 1.0)}
+    for dtype in dt.GROUPS[ol.CHECKED_OPS[op]]:
+        rng = np.random.default_rng(zlib.crc32(("%s %s c" % (op, dtype)).encode()))
+        es = dt.SIZE[dtype]
+        tol = unary_tolerance(op, dtype)
+        for name, size, v1, vout in layouts(dtype):
+            if name in ("row_broadcast", "scalar_broadcast"):
+                continue
+            for kind in ("inside", "outside", "nan"):
+                inside_kind = {"arcsin": "unit", "arccos": "unit", "arctanh": "unit"}.get(op, "positive")
+                a = util.fill_buffer(v1, rng, inside_kind)
+                vals = util.gather(a, v1).copy()
+                if op == "arccosh":
+                    vals = (sn_half(vals, dtype, lambda f: f + 1.0))
+                if vals.size and kind != "inside":
+                    pos = int(rng.integers(0, vals.size))
+                    bad = {"outside": {"arcsin": 1.5, "arccos": -1.5, "arctanh": 2.0, "arccosh": 0.5, "log1p": -1.5,
+                                       "reciprocal": 0.0}.get(op, -0.25), "nan": float("nan")}[kind]
+                    vals = sn_half(vals, dtype, lambda f: np.where(np.arange(f.size) == pos, bad, f))
+                a = scatter_into(a, v1, vals)
+                dst0 = util.fill_buffer(vout, rng, "general")
+                want = dst0.copy()
+                cpu.unary(op, dtype, size, v1.strides, a.ctypes.data + v1.offset, vout.strides, want.ctypes.data + vout.offset)
+                if op in bounds:
+                    red, b = bounds[op]
+                    ok = cpu.reduce_all(red, dtype, size, v1.strides, a.ctypes.data + v1.offset,
+                                        bounds=(scalar_of(b, dtype),))[0]
+                elif op == "reciprocal":
+                    ok = cpu.reduce_all("all", dtype, size, v1.strides, a.ctypes.data + v1.offset)[0]
+                else:
+                    ok = cpu.reduce_all("all_gele", dtype, size, v1.strides, a.ctypes.data + v1.offset,
+                                        bounds=(scalar_of(-1.0, dtype), scalar_of(1.0, dtype)))[0]
+                # the data does what the case says (a NaN fails none of the reference's comparisons)
+                expect_ok = kind != "outside" or vals.size == 0
+                assert bool(ok) == expect_ok, ("test data", op, dtype, name, kind)
+                da, dd = dev.upload(a), dev.upload(dst0)
+                flag = dev.empty(16)
+                gpu.unary_checked(op, dtype, size, v1.strides, da.data_ptr() + v1.offset, vout.strides,
+                                  dd.data_ptr() + vout.offset, flag.data_ptr(), dev.stream)
+                got = dev.download(dd)
+                what = "%s_checked_%s %s %s" % (op, dtype, name, kind)
+                util.assert_same(util.gather(got, vout), util.gather(want, vout), dtype, tol, what)
+                assert int(dev.download(flag)[:4].view(np.int32)[0]) == (0 if ok else 1), what
+
+
+def sn_half(vals, dtype, fn):
+    """Apply fn to the values as float64 and return them in the carrier of dtype (half through the oracle's rounding)."""
+    from oracle import solid_numpy as sn
+    if dtype == "half":
+        f = sn.half_to_float(vals).astype(np.float64)
+        return sn.float_to_half(np.asarray(fn(f), dtype=np.float32))
+    return np.asarray(fn(vals.astype(np.float64))).astype(vals.dtype)
+
+
+def scatter_into(buf, view, vals):
+    """Write the elements of `vals` (logical column-major order of the view) back into a copy of the byte buffer."""
+    out = buf.copy()
+    es = dt.SIZE[view.dtype]
+    raw = np.ascontiguousarray(vals).view(np.uint8).reshape(-1, es)
+    idx = np.zeros(1, dtype=np.int64)
+    for d in range(len(view.size) - 1, -1, -1):
+        idx = (idx[:, None] + (np.arange(view.size[d], dtype=np.int64) * view.strides[d])[None, :]).reshape(-1)
+    if raw.shape[0]:
+        out[(view.offset + idx)[:, None] + np.arange(es)[None, :]] = raw
+    return out
+
+
+def scalar_of(value, dtype):
+    from solid_b200 import ops
+    return ops.scalar_bytes(value, dtype)
