@@ -174,6 +174,12 @@
 #define SOLID_GPU_ARGS_INDEX_TO_OFFSET \
    int nstrides, solid_int64 *strides, ptrdiff_t strideReduce, size_t nelem, \
    ptrdiff_t stride1, void *ptr1, ptrdiff_t stride2, void *ptr2, cudaStream_t stream
+#define SOLID_GPU_ARGS_GEMM \
+   char transA, char transB, size_t M, size_t N, size_t K, void *ptrAlpha, void *ptrA, ptrdiff_t ldA, \
+   void *ptrB, ptrdiff_t ldB, void *ptrBeta, void *ptrC, ptrdiff_t ldC, int scalarModeHost, cudaStream_t stream
+#define SOLID_GPU_ARGS_GEMM_WITH_PLAN \
+   solid_gpu_gemm_plan *plan, void *ptrAlpha, void *ptrA, ptrdiff_t ldA, void *ptrB, ptrdiff_t ldB, \
+   void *ptrBeta, void *ptrC, ptrdiff_t ldC, int scalarModeHost, cudaStream_t stream
 #define SOLID_GPU_ARGS_COPY \
    int ndims1, const size_t *size1, const ptrdiff_t *strides1, void *ptr1, \
    int ndims2, const size_t *size2, const ptrdiff_t *strides2, void *ptr2, \
@@ -258,6 +264,27 @@ SOLID_GPU_DECLARE_(add_if_negative, sint)
 #undef SOLID_GPU_ARGS_CURRENT_
 #define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_INDEX_TO_OFFSET
 SOLID_GPU_DECLARE_(index_to_offset, integer)
+#undef SOLID_GPU_ARGS_CURRENT_
+
+/* Integer and boolean matrix product C = alpha * op(A) * op(B) + beta * C in the wrap-around arithmetic of the     */
+/* element type (bool: and / or) -- solid_core_gpu.src:415-440, template_blas.cu:26-259.  Column-major, leading     */
+/* dimensions in elements, trans 'N' or 'T'; alpha and beta are read from HOST memory when scalarModeHost is set,   */
+/* from DEVICE memory otherwise; a NULL scalar stands for alpha = 1, beta = 0.  The plan has the reference's layout. */
+typedef struct
+{  char    transA, transB;
+   size_t  M, N, K;
+   dim3    gridsize;
+   dim3    blocksize;
+   int     tilesize;
+   int     sharedmem;
+} solid_gpu_gemm_plan;
+SOLID_API int solid_gpu_gemm_create_plan(char transA, char transB, size_t M, size_t N, size_t K,
+                                         int elemsize, int device, solid_gpu_gemm_plan *plan);
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_GEMM
+SOLID_GPU_DECLARE_(gemm, integer_bool)
+#undef SOLID_GPU_ARGS_CURRENT_
+#define SOLID_GPU_ARGS_CURRENT_ SOLID_GPU_ARGS_GEMM_WITH_PLAN
+SOLID_GPU_DECLARE_(gemm_with_plan, integer_bool)
 #undef SOLID_GPU_ARGS_CURRENT_
 
 /* strides2 == NULL and ptr2 == NULL: in place */

@@ -29,6 +29,8 @@ SOLID_GPU_SCALAR_OPS(SD_DEFINE_LUT)
 SD_DEFINE_LUT(steps_int64, all)
 SD_DEFINE_LUT(steps_double, all)
 SD_DEFINE_LUT(steps_cdouble, complex)
+SD_DEFINE_LUT(gemm, integer_bool)
+SD_DEFINE_LUT(gemm_with_plan, integer_bool)
 SD_DEFINE_LUT(get_index, all)
 SD_DEFINE_LUT(set_index, all)
 SD_DEFINE_LUT(fill_index, all)

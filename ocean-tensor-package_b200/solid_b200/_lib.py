@@ -158,6 +158,16 @@ class SolidGPU:
         self._check(f(C.c_int(len(size)), _sizes(size), _strides(strides1), C.c_void_p(ptr1), st2, C.c_void_p(ptr2),
                       C.c_void_p(flag_ptr), C.c_void_p(stream)), "%s_checked_%s" % (name, dtype))
 
+    def gemm(self, dtype, trans_a, trans_b, m, n, k, alpha_ptr, a_ptr, lda, b_ptr, ldb, beta_ptr, c_ptr, ldc,
+             scalars_on_host=True, stream=0):
+        """C = alpha * op(A) * op(B) + beta * C for the integer types and bool; leading dimensions in elements;
+        alpha_ptr / beta_ptr are host addresses (scalars_on_host) or device addresses, None for 1 and 0."""
+        f = self.fn("solid_gpu_gemm_%s" % dtype)
+        self._check(f(C.c_char(trans_a.encode()), C.c_char(trans_b.encode()), C.c_size_t(m), C.c_size_t(n), C.c_size_t(k),
+                      C.c_void_p(alpha_ptr), C.c_void_p(a_ptr), C.c_ssize_t(lda), C.c_void_p(b_ptr), C.c_ssize_t(ldb),
+                      C.c_void_p(beta_ptr), C.c_void_p(c_ptr), C.c_ssize_t(ldc), C.c_int(1 if scalars_on_host else 0),
+                      C.c_void_p(stream)), "gemm_%s" % dtype)
+
     # -- indexed access ----------------------------------------------------------------
     def index2(self, name, dtype, size, offsets, strides1, ptr1, strides2, ptr2, stream=0):
         """name 'get_index' (ptr2 = ptr1[index]) or 'set_index' (ptr1[index] = ptr2); offsets: per dimension a

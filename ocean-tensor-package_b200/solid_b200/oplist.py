@@ -25,6 +25,7 @@ COMPARE_OPS = ["lt", "le", "ge", "gt", "eq", "ne"]
 # unary functions fused with their domain test: name -> (type group, reference test)
 CHECKED_OPS = {"sqrt": "real", "log": "real", "log2": "real", "log10": "real", "log1p": "real", "arccosh": "real",
                "arcsin": "real", "arccos": "real", "arctanh": "real", "reciprocal": "real"}
+GEMM_OPS = {"gemm": "integer_bool", "gemm_with_plan": "integer_bool"}
 INDEX_OPS = {"get_index": "all", "set_index": "all", "fill_index": "all", "add_if_negative": "sint",
              "index_to_offset": "integer"}
 STEPS_OPS = {"steps_int64": "all", "steps_double": "all", "steps_cdouble": "complex"}

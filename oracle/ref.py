@@ -125,6 +125,13 @@ class SolidCPU:
             C.c_int(len(strides)), arr, C.c_ssize_t(stride_reduce), C.c_size_t(nelem), C.c_ssize_t(stride1),
             C.c_void_p(ptr1), C.c_ssize_t(stride2), C.c_void_p(ptr2)), "index_to_offset")
 
+    def gemm(self, dtype, trans_a, trans_b, m, n, k, alpha_ptr, a_ptr, lda, b_ptr, ldb, beta_ptr, c_ptr, ldc):
+        """solid_cpu_gemm_<dtype> (solid/src/core/cpu/template_blas.c): integer types and bool."""
+        self._check(self.fn("solid_cpu_gemm_%s" % dtype)(
+            C.c_char(trans_a.encode()), C.c_char(trans_b.encode()), C.c_size_t(m), C.c_size_t(n), C.c_size_t(k),
+            C.c_void_p(alpha_ptr), C.c_void_p(a_ptr), C.c_ssize_t(lda), C.c_void_p(b_ptr), C.c_ssize_t(ldb),
+            C.c_void_p(beta_ptr), C.c_void_p(c_ptr), C.c_ssize_t(ldc)), "gemm")
+
     def byteswap(self, dtype, size, strides, ptr):
         self._check(self.fn("solid_cpu_byteswap_%s" % dtype)(
             C.c_int(len(size)), _sizes(size), _strides(strides), C.c_void_p(ptr)), "byteswap")

@@ -42,7 +42,7 @@ def test_library_exports_every_declared_symbol(declared):
 def expected_functions():
     names = set()
     families = [ol.FILL_OPS, {"masked_fill": "all", "byteswap": "all", "axpy": "real"}, ol.UNARY_OPS, ol.BINARY_OPS,
-                {op + "_scalar": group for op, group in ol.SCALAR_OPS.items()}, ol.STEPS_OPS, ol.INDEX_OPS, {op + "_checked": g for op, g in ol.CHECKED_OPS.items()}, ol.REDUCE_BOOL_OPS, ol.REDUCE_BOUND1_OPS, ol.REDUCE_BOUND2_OPS, ol.REDUCE_U64_OPS,
+                {op + "_scalar": group for op, group in ol.SCALAR_OPS.items()}, ol.STEPS_OPS, ol.GEMM_OPS, ol.INDEX_OPS, {op + "_checked": g for op, g in ol.CHECKED_OPS.items()}, ol.REDUCE_BOOL_OPS, ol.REDUCE_BOUND1_OPS, ol.REDUCE_BOUND2_OPS, ol.REDUCE_U64_OPS,
                 ol.REDUCE_VOID_OPS, ol.REDUCE_NORM_OPS, ol.AXIS_OPS, ol.AXIS_NORM_OPS]
     for fam in families:
         for op, group in fam.items():
@@ -67,7 +67,7 @@ def test_python_operation_lists_match_the_header(declared):
 def test_function_tables_have_entries_and_holes():
     lib = _lib.get()
     families = [ol.FILL_OPS, {"masked_fill": "all", "byteswap": "all", "axpy": "real"}, ol.UNARY_OPS, ol.BINARY_OPS,
-                {op + "_scalar": group for op, group in ol.SCALAR_OPS.items()}, ol.STEPS_OPS, ol.INDEX_OPS, {op + "_checked": g for op, g in ol.CHECKED_OPS.items()}, ol.REDUCE_BOOL_OPS, ol.REDUCE_BOUND1_OPS, ol.REDUCE_BOUND2_OPS, ol.REDUCE_U64_OPS,
+                {op + "_scalar": group for op, group in ol.SCALAR_OPS.items()}, ol.STEPS_OPS, ol.GEMM_OPS, ol.INDEX_OPS, {op + "_checked": g for op, g in ol.CHECKED_OPS.items()}, ol.REDUCE_BOOL_OPS, ol.REDUCE_BOUND1_OPS, ol.REDUCE_BOUND2_OPS, ol.REDUCE_U64_OPS,
                 ol.REDUCE_VOID_OPS, ol.REDUCE_NORM_OPS, ol.AXIS_OPS, ol.AXIS_NORM_OPS]
     for fam in families:
         for op, group in fam.items():
