@@ -92,6 +92,22 @@ SOLID_API int OcTensorGPU_stepsInt64(const OcTensorView *tensor, solid_int64 off
 SOLID_API int OcTensorGPU_stepsDouble(const OcTensorView *tensor, solid_double offset, solid_double step);
 SOLID_API int OcTensorGPU_stepsCDouble(const OcTensorView *tensor, solid_cdouble offset, solid_cdouble step);
 
+/* Indexed access (src/core/gpu/op/tensor_index_gpu.c:58-260).  An index view is the indexed tensor plus, per         */
+/* dimension, either NULL (the dimension is addressed by its stride) or a 1-D contiguous int64 tensor on the same     */
+/* device holding one BYTE offset per selected position; `size` is the shape of the selection.                        */
+typedef struct {
+   OcTensorView        view;          /* the indexed tensor (its strides serve the dimensions without a table)      */
+   int                 ndims;         /* dimensions of the selection                                                 */
+   size_t              size[8];       /* shape of the selection                                                      */
+   const OcTensorView *offsets[8];    /* per dimension: NULL or the table                                            */
+} OcIndexView;
+SOLID_API int OcTensorGPU_getIndex(const OcIndexView *index, const OcTensorView *dst);        /* dst = view[index]   */
+SOLID_API int OcTensorGPU_setIndex(const OcIndexView *index, const OcTensorView *src);        /* view[index] = src   */
+SOLID_API int OcTensorGPU_fillIndex(const OcIndexView *index, const OcScalarView *scalar);    /* view[index] = value */
+SOLID_API int OcTensorGPU_addIfNegative(const OcTensorView *tensor, const OcScalarView *scalar);
+/* tensor: nstrides x nelem (or 1-D: nelem) integer indices; offsets: nelem int64 results, sum strides[i] * index[i] */
+SOLID_API int OcTensorGPU_indexToOffset(const OcTensorView *tensor, const solid_int64 *strides, const OcTensorView *offsets);
+
 SOLID_API int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst);
 SOLID_API int OcTensorGPU_byteswapNoFlag(const OcTensorView *tensor);   /* reverses the stored bytes in place */
 SOLID_API int OcTensorGPU_fill(const OcTensorView *tensor, const OcScalarView *scalar);

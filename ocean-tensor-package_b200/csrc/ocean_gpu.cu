@@ -257,6 +257,104 @@ OCGPU_DEFINE_STEPS(stepsInt64, steps_int64, solid_int64)
 OCGPU_DEFINE_STEPS(stepsDouble, steps_double, solid_double)
 OCGPU_DEFINE_STEPS(stepsCDouble, steps_cdouble, solid_cdouble)
 
+// ---------------------------------------------------------------------------------- indexed access
+static int index_prepare(const OcIndexView *ix, const OcTensorView *other, const char *what, solid_int64 **tables)
+{
+   if (ix == nullptr) return fail("Missing index view in %s", what);
+   if (check_elemwise(&ix->view, "indexed") != 0) return -1;
+   if (ix->ndims < 0 || ix->ndims > 8) return fail("Invalid number of index dimensions in %s", what);
+   if (ix->ndims != ix->view.ndims) return fail("The index must cover every dimension of the tensor in %s", what);
+   for (int d = 0; d < ix->ndims; d++) {
+      const OcTensorView *t = ix->offsets[d];
+      tables[d] = nullptr;
+      if (t == nullptr) continue;
+      if (check_view(t, "offset") != 0) return -1;
+      if (t->dtype != SD_INT64 || t->ndims != 1 || t->size[0] != ix->size[d] || (t->size[0] > 1 && t->strides[0] != 8) || t->byteswapped)
+         return fail("Offset tables must be contiguous native int64 vectors with one entry per selected position");
+      if (t->device != ix->view.device) return fail("Offset tables must be on the device of the indexed tensor");
+      tables[d] = (solid_int64 *)t->data;
+   }
+   if (other) {
+      if (other->ndims != ix->ndims) return fail("Tensor size mismatch in %s", what);
+      for (int d = 0; d < ix->ndims; d++) if (other->size[d] != ix->size[d]) return fail("Tensor size mismatch in %s", what);
+      if (other->dtype != ix->view.dtype) return fail("Data type mismatch in %s", what);
+      if (other->device != ix->view.device) return fail("Device mismatch in %s", what);
+   }
+   return 0;
+}
+static int index_tables_wait(const OcTensorView *writer, const OcIndexView *ix, bool before)
+{
+   for (int d = 0; d < ix->ndims; d++) {
+      if (ix->offsets[d] == nullptr) continue;
+      if ((before ? start_read(writer, ix->offsets[d]) : finish_read(writer, ix->offsets[d])) != 0) return -1;
+   }
+   return 0;
+}
+
+extern "C" int OcTensorGPU_getIndex(const OcIndexView *ix, const OcTensorView *dst)
+{
+   solid_int64 *tables[8];
+   if (check_elemwise(dst, "destination") != 0 || index_prepare(ix, dst, "getIndex", tables) != 0) return -1;
+   solid_funptr_gpu_get_index f = lookup(solid_gpu_get_index, dst->dtype, "getIndex");
+   if (f == nullptr || set_device(dst->device) != 0) return -1;
+   if (start_read(dst, &ix->view) != 0 || index_tables_wait(dst, ix, true) != 0) return -1;
+   if (f(ix->ndims, ix->size, tables, ix->view.strides, ix->view.data, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+   if (update(dst) != 0 || finish_read(dst, &ix->view) != 0) return -1;
+   return index_tables_wait(dst, ix, false);
+}
+extern "C" int OcTensorGPU_setIndex(const OcIndexView *ix, const OcTensorView *src)
+{
+   solid_int64 *tables[8];
+   if (check_elemwise(src, "source") != 0 || index_prepare(ix, src, "setIndex", tables) != 0) return -1;
+   const OcTensorView *dst = &ix->view;
+   solid_funptr_gpu_set_index f = lookup(solid_gpu_set_index, dst->dtype, "setIndex");
+   if (f == nullptr || set_device(dst->device) != 0) return -1;
+   if (start_read(dst, src) != 0 || index_tables_wait(dst, ix, true) != 0) return -1;
+   if (f(ix->ndims, ix->size, tables, dst->strides, dst->data, src->strides, src->data, dst->stream) != 0) return fail_solid();
+   if (update(dst) != 0 || finish_read(dst, src) != 0) return -1;
+   return index_tables_wait(dst, ix, false);
+}
+extern "C" int OcTensorGPU_fillIndex(const OcIndexView *ix, const OcScalarView *s)
+{
+   solid_int64 *tables[8];
+   if (index_prepare(ix, nullptr, "fillIndex", tables) != 0) return -1;
+   const OcTensorView *dst = &ix->view;
+   if (s == nullptr || s->dtype != dst->dtype) return fail("The scalar must have the data type of the tensor");
+   solid_funptr_gpu_fill_index f = lookup(solid_gpu_fill_index, dst->dtype, "fillIndex");
+   if (f == nullptr || set_device(dst->device) != 0) return -1;
+   if (index_tables_wait(dst, ix, true) != 0) return -1;
+   if (f(ix->ndims, ix->size, tables, dst->strides, dst->data, s->value, dst->stream) != 0) return fail_solid();
+   if (update(dst) != 0) return -1;
+   return index_tables_wait(dst, ix, false);
+}
+extern "C" int OcTensorGPU_addIfNegative(const OcTensorView *t, const OcScalarView *s)
+{
+   if (check_elemwise(t, "input") != 0) return -1;
+   if (s == nullptr || s->dtype != t->dtype) return fail("The scalar must have the data type of the tensor");
+   solid_funptr_gpu_add_if_negative f = lookup(solid_gpu_add_if_negative, t->dtype, "addIfNegative");
+   if (f == nullptr || set_device(t->device) != 0) return -1;
+   if (f(t->ndims, t->size, t->strides, t->data, s->value, t->stream) != 0) return fail_solid();
+   return update(t);
+}
+extern "C" int OcTensorGPU_indexToOffset(const OcTensorView *t, const solid_int64 *strides, const OcTensorView *offsets)
+{
+   if (check_elemwise(t, "index") != 0 || check_elemwise(offsets, "offset") != 0) return -1;
+   if (strides == nullptr) return fail("Missing strides in indexToOffset");
+   if (offsets->dtype != SD_INT64 || offsets->ndims != 1) return fail("The offsets must be a vector of int64");
+   if (t->ndims != 1 && t->ndims != 2) return fail("The index tensor must have one or two dimensions");
+   solid_funptr_gpu_index_to_offset f = lookup(solid_gpu_index_to_offset, t->dtype, "indexToOffset");
+   if (f == nullptr || set_device(offsets->device) != 0) return -1;
+   ptrdiff_t stride1, stride_reduce; size_t nelem; int nstrides;           // tensor_index_gpu.c:107-118
+   if (t->ndims == 1) { stride1 = t->strides[0]; stride_reduce = 0; nstrides = 1; nelem = t->size[0]; }
+   else { stride1 = t->strides[1]; stride_reduce = t->strides[0]; nstrides = (int)t->size[0]; nelem = t->size[1]; }
+   if (offsets->size[0] != nelem) return fail("Tensor size mismatch in indexToOffset");
+   if (start_read(offsets, t) != 0) return -1;
+   if (f(nstrides, const_cast<solid_int64 *>(strides), stride_reduce, nelem, stride1, t->data,
+         offsets->strides[0], offsets->data, offsets->stream) != 0) return fail_solid();
+   if (update(offsets) != 0) return -1;
+   return finish_read(offsets, t);
+}
+
 // Can kernels on device `reader` load memory of device `owner`?  Asked of the runtime once per pair; peer access is
 // switched on at that moment (another library in the process may have done so already, which is not an error).
 static bool peer_readable(int reader, int owner)

@@ -22,6 +22,12 @@ class TensorView(C.Structure):
                 ("stream", C.c_void_p), ("event", C.c_void_p)]
 
 
+class IndexView(C.Structure):
+    """OcIndexView: the indexed tensor, the shape of the selection and per dimension NULL or an offset table."""
+    _fields_ = [("view", TensorView), ("ndims", C.c_int), ("size", C.c_size_t * 8),
+                ("offsets", C.POINTER(TensorView) * 8)]
+
+
 class ScalarView(C.Structure):
     _fields_ = [("dtype", C.c_int), ("value", Scalar)]
 

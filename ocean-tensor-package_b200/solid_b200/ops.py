@@ -408,3 +408,60 @@ def axpy_sums(a, x: Tensor, y: Tensor, z: Tensor | None = None, sums=None):
     part = _scratch_buffer(x.storage.device, lib.axpy_sums_buffer_size(x.device_index, x.nelem))
     lib.axpy_sums(x.dtype, x.nelem, scalar_bytes(a, x.dtype), x.ptr, y.ptr, z.ptr, sums.data_ptr(), part.data_ptr(), _stream(x))
     return z, sums
+
+
+# ----------------------------------------------------------------------------
+# indexed access (Ocean's tensor[index] with integer index lists)
+# ----------------------------------------------------------------------------
+def _index_view(t: Tensor, positions):
+    """OcIndexView for `t` and one entry per dimension: None (every position, by stride) or a sequence of integer
+    positions (negative ones count from the end).  Returns the view, the selection shape and the objects to keep."""
+    import ctypes as C
+    oc = _ocean.get()
+    if len(positions) != t.ndims:
+        raise ValueError("one index entry per dimension is needed")
+    ix = _ocean.IndexView()
+    ix.view = oc.view(t, _stream(t))
+    ix.ndims = t.ndims
+    keep, shape = [], []
+    for d, pos in enumerate(positions):
+        if pos is None:
+            ix.size[d] = t.size[d]; shape.append(t.size[d])
+            continue
+        p = np.asarray(pos, dtype=np.int64).reshape(-1)
+        p = np.where(p < 0, p + t.size[d], p)
+        if p.size and (p.min() < 0 or p.max() >= t.size[d]):
+            raise IndexError("index out of range in dimension %d" % d)
+        table = Tensor.from_numpy(p * t.strides[d], "int64", t.storage.device)
+        tv = oc.view(table, _stream(t))
+        keep += [table, tv]
+        ix.offsets[d] = C.pointer(tv)
+        ix.size[d] = p.size; shape.append(int(p.size))
+    return ix, shape, keep
+
+
+def take(t: Tensor, positions, dst: Tensor | None = None) -> Tensor:
+    """dst = t[positions] (outer product of the per-dimension index lists)."""
+    import ctypes as C
+    t = _native(t)
+    ix, shape, keep = _index_view(t, positions)
+    out = dst if dst is not None else Tensor.empty(shape, t.dtype, t.storage.device)
+    _dispatch("getIndex", C.byref(ix), out)
+    return out
+
+
+def put(t: Tensor, positions, src: Tensor) -> Tensor:
+    """t[positions] = src (positions must not repeat)."""
+    import ctypes as C
+    ix, shape, keep = _index_view(t, positions)
+    _dispatch("setIndex", C.byref(ix), _native(src) if src.dtype == t.dtype else cast(src, t.dtype))
+    return t
+
+
+def fill_at(t: Tensor, positions, value) -> Tensor:
+    """t[positions] = value."""
+    import ctypes as C
+    ix, shape, keep = _index_view(t, positions)
+    sv = _ocean.get().scalar(scalar_bytes(value, t.dtype), t.dtype)
+    _dispatch("fillIndex", C.byref(ix), C.byref(sv))
+    return t

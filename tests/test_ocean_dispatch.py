@@ -170,6 +170,46 @@ def test_ranges_count_in_memory_order(gpu):
 
 
 @pytest.mark.gpu
+def test_indexed_access_through_the_dispatch(gpu):
+    """OcTensorGPU_getIndex / setIndex / fillIndex / addIfNegative / indexToOffset against numpy's outer indexing."""
+    from solid_b200 import Tensor, ops
+    import ctypes as C
+    oc = _ocean.get(); oc.init()
+    rng = np.random.default_rng(21)
+    a = rng.normal(size=(40, 30, 5)).astype(np.float32)
+    t = Tensor.from_numpy(a)
+    rows = rng.permutation(40)[:17]; planes = np.array([4, -1, 0])
+    got = ops.take(t, [rows, None, planes]).numpy()
+    assert np.array_equal(got, a[np.ix_(rows, np.arange(30), planes % 5)])
+    tt = t.T                                                    # a view with permuted strides
+    got = ops.take(tt, [planes, None, rows]).numpy()
+    assert np.array_equal(got, a.transpose(2, 1, 0)[np.ix_(planes % 5, np.arange(30), rows)])
+    vals = rng.normal(size=(17, 30, 3)).astype(np.float32)
+    ops.put(t, [rows, None, [4, 3, 0]], Tensor.from_numpy(vals))
+    want = a.copy(); want[np.ix_(rows, np.arange(30), [4, 3, 0])] = vals
+    assert np.array_equal(t.numpy(), want)
+    ops.fill_at(t, [[0, 0, 39], [1, 1], None], -7.5)
+    want[np.ix_([0, 39], [1], np.arange(5))] = -7.5
+    assert np.array_equal(t.numpy(), want)
+    with pytest.raises(IndexError):
+        ops.take(t, [[40], None, None])
+    # negative indices wrapped on the device, then turned into offsets
+    idx = np.asfortranarray(np.array([[3, -1, 0, 39], [-30, 29, 5, -2]], dtype=np.int64))      # 2 x 4 index tuples
+    ti = Tensor.from_numpy(idx)
+    for d, n in enumerate((40, 30)):
+        row = ti.slice(0, d, d + 1)
+        sv = oc.scalar(np.int64(n).tobytes(), "int64")
+        rv = oc.view(row, 0)
+        oc._check(oc.fn("addIfNegative")(C.byref(rv), C.byref(sv)), "addIfNegative")
+    off = Tensor.empty([4], "int64")
+    strides = (C.c_int64 * 2)(4, 160)
+    tv, ov = oc.view(ti, 0), oc.view(off, 0)
+    oc._check(oc.fn("indexToOffset")(C.byref(tv), strides, C.byref(ov)), "indexToOffset")
+    wrapped = np.where(idx < 0, idx + np.array([[40], [30]]), idx)
+    assert np.array_equal(off.numpy(), 4 * wrapped[0] + 160 * wrapped[1])
+
+
+@pytest.mark.gpu
 def test_stream_protocol_orders_producer_and_consumer(gpu):
     """The source is produced on one stream, the operation runs on the destination's stream: the
     dispatch must wait for the source's event, and record the destination's."""
