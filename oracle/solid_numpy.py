@@ -667,3 +667,27 @@ def index_to_offset(index: np.ndarray, strides) -> np.ndarray:
     """index[i, e] (component i of tuple e) -> sum_i strides[i] * index[i, e] as int64."""
     with np.errstate(over="ignore"):
         return (np.asarray(strides, dtype=np.int64)[:, None] * index.astype(np.int64)).sum(axis=0, dtype=np.int64)
+
+
+def gemm(dtype: str, trans_a: str, trans_b: str, m: int, n: int, k: int, alpha, A, lda: int, B, ldb: int,
+         beta, C, ldc: int) -> np.ndarray:
+    """C = alpha * op(A) * op(B) + beta * C for the integer types and bool (solid/src/core/cpu/template_blas.c:30-314):
+    column-major buffers with leading dimensions in elements, wrap-around arithmetic of the element type, and / or
+    for bool.  Returns the updated copy of the C buffer."""
+    npdt = NP[dtype]
+    def mat(buf, rows, cols, ld):
+        return np.asarray(buf).reshape(-1)[: ld * max(cols, 1)].reshape(max(cols, 1), ld).T[:rows, :cols]
+    a = mat(A, m, k, lda) if trans_a in "nN" else mat(A, k, m, lda).T
+    b = mat(B, k, n, ldb) if trans_b in "nN" else mat(B, n, k, ldb).T
+    out = np.array(C, dtype=npdt).reshape(-1).copy()
+    c = out[: ldc * max(n, 1)].reshape(max(n, 1), ldc).T[:m, :n]          # a view into `out`
+    if dtype == "bool":
+        prod = (a.astype(np.uint8)[:, :, None] & b.astype(np.uint8)[None, :, :]).any(axis=1).astype(np.uint8) if k else np.zeros((m, n), np.uint8)
+        c[...] = (np.uint8(alpha) & prod) | (np.uint8(beta) & c)
+        return out
+    wide = np.uint64
+    with np.errstate(over="ignore"):
+        prod = a.astype(np.int64).astype(wide) @ b.astype(np.int64).astype(wide) if k else np.zeros((m, n), wide)
+        res = np.int64(alpha).astype(wide) * prod + np.int64(beta).astype(wide) * c.astype(np.int64).astype(wide)
+        c[...] = res.astype(npdt) if npdt in (np.uint64,) else res.astype(np.int64).astype(npdt)
+    return out

@@ -93,6 +93,39 @@ def main():
             raw = cpu.reduce_all(op, dtype, [n], [dt.SIZE[dtype]], x.ctypes.data)
             out["reduce/%s/%s/in" % (op, dtype)] = x
             out["reduce/%s/%s/out" % (op, dtype)] = np.frombuffer(raw[: dt.SIZE[rtype]], dtype=dt.NUMPY[rtype]).copy()
+    # ranges: offset + i * step in int64 / double (/ complex double) for every element type
+    for dtype in dt.NAMES:
+        es = dt.SIZE[dtype]
+        kinds = [("int64", 7, 3), ("int64", -5, 2), ("double", 0.25, 0.5)]
+        if dtype not in dt.UINT and dtype != "bool":
+            kinds.append(("double", 100.0, -0.375))             # negative double -> unsigned is undefined in C
+        if dtype in dt.COMPLEX:
+            kinds.append(("cdouble", 1 - 2j, 0.5 + 0.25j))
+        for j, (kind, off, step) in enumerate(kinds):
+            buf = np.zeros(N * es, dtype=np.uint8)
+            cpu.steps(kind, dtype, [N], [es], buf.ctypes.data, off, step)
+            out["steps/%s/%s/%d/param" % (kind, dtype, j)] = np.array([complex(off), complex(step)])
+            out["steps/%s/%s/%d/out" % (kind, dtype, j)] = buf
+    # integer and boolean matrix products (column-major, padded leading dimensions)
+    for dtype in dt.GROUPS["integer_bool"]:
+        rng = np.random.default_rng(seed("g", dtype))
+        npdt = dt.NUMPY[dtype]
+        m, n, k = 7, 5, 9
+        for ta in "NT":
+            for tb in "NT":
+                ra, ca = (m, k) if ta == "N" else (k, m)
+                rb, cb = (k, n) if tb == "N" else (n, k)
+                lda, ldb, ldc = ra + 2, rb + 1, m + 3
+                draw = (lambda cnt: (rng.random(cnt) < 0.4).astype(np.uint8)) if dtype == "bool" else \
+                       (lambda cnt: rng.integers(0 if dtype in dt.UINT else -9, 10, cnt).astype(npdt))
+                A, B, C0 = draw(lda * ca), draw(ldb * cb), draw(ldc * n)
+                alpha, beta = (1, 1) if dtype == "bool" else (3, 2)
+                al, be = np.array([alpha]).astype(npdt), np.array([beta]).astype(npdt)
+                Cw = C0.copy()
+                cpu.gemm(dtype, ta, tb, m, n, k, al.ctypes.data, A.ctypes.data, lda, B.ctypes.data, ldb, be.ctypes.data, Cw.ctypes.data, ldc)
+                key = "gemm/%s%s/%s" % (ta, tb, dtype)
+                out[key + "/A"], out[key + "/B"], out[key + "/C"], out[key + "/out"] = A, B, C0, Cw
+                out[key + "/param"] = np.array([m, n, k, lda, ldb, ldc, alpha, beta], dtype=np.int64)
     path = Path(__file__).resolve().parent / "solid_cpu_golden.npz"
     np.savez_compressed(path, **out)
     print("wrote %s: %d arrays, %.1f KiB" % (path, len(out), path.stat().st_size / 1024))

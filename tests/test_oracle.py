@@ -216,3 +216,29 @@ def test_ranges_and_indexed_access_match_reference_library(cpu):
         out = np.zeros(200, dtype=np.int64)
         cpu.index_to_offset(dtype, strides, es, 200, 3 * es, idx.ctypes.data, 8, out.ctypes.data)
         assert np.array_equal(sn.index_to_offset(idx, strides), out), dtype
+
+
+def test_golden_steps_and_gemm(golden):
+    """Ranges and integer / bool matrix products of the numpy restatement against the committed outputs of the
+    reference's Solid CPU library."""
+    checked = 0
+    for key in sorted(k for k in golden.files if k.startswith("steps/") and k.endswith("/out")):
+        _, kind, dtype, j, _ = key.split("/")
+        off, step = golden["steps/%s/%s/%s/param" % (kind, dtype, j)]
+        if kind == "int64":
+            off, step = int(off.real), int(step.real)
+        elif kind == "double":
+            off, step = float(off.real), float(step.real)
+        want = golden[key]
+        n = want.size // dt.SIZE[dtype]
+        assert sn.steps(kind, dtype, n, off, step).tobytes() == want.tobytes(), key
+        checked += 1
+    for key in sorted(k for k in golden.files if k.startswith("gemm/") and k.endswith("/out")):
+        _, trans, dtype, _ = key.split("/")
+        base = key[: -len("/out")]
+        m, n, k, lda, ldb, ldc, alpha, beta = (int(v) for v in golden[base + "/param"])
+        got = sn.gemm(dtype, trans[0], trans[1], m, n, k, alpha, golden[base + "/A"], lda, golden[base + "/B"], ldb,
+                      beta, golden[base + "/C"], ldc)
+        assert np.array_equal(got, golden[key]), key
+        checked += 1
+    assert checked > 80
