@@ -50,7 +50,8 @@ def run_pair(gpu, dev, shape, axes, seed):
     arr = util.gather(buf, v).reshape(shape, order="F").astype(np.float64)
     want = arr.sum(axis=tuple(axes)).reshape(-1, order="F")
     n = int(np.prod(rsize))
-    assert np.all(np.abs(outs[1].astype(np.float64) - want) <= 1e-5 * np.sqrt(n) * np.abs(arr).sum(axis=tuple(axes)).max())
+    bound = util.accumulation_bound(n, "float", np.abs(arr).sum(axis=tuple(axes)).reshape(-1, order="F"))
+    assert np.all(np.abs(outs[1].astype(np.float64) - want) <= bound)
     return cfg.bufferSize, outs
 
 

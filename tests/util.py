@@ -201,3 +201,71 @@ def assert_same(got: np.ndarray, want: np.ndarray, dtype: str, ulp: int = 0, wha
     assert bad.size == 0, "%s: %d elements beyond %d ulp (max %d), first component %d: got %r want %r" % (
         what, bad.size, ulp, int(d.max()), bad[0],
         as_float_components(got, dtype)[bad[0]], as_float_components(want, dtype)[bad[0]])
+
+
+# ----------------------------------------------------------------------------
+# floating-point accumulations against a float64 evaluation
+# ----------------------------------------------------------------------------
+TIGHT_ACCUM = {"sum", "sum_nan", "sum_abs", "sum_abs_nan", "norm2", "norm2_nan"}
+
+
+def as_values(arr: np.ndarray, dtype: str) -> np.ndarray:
+    """Elements as float64 (real types, integers included) or complex128."""
+    if dtype in dt.COMPLEX:
+        c = as_float_components(arr, dtype).reshape(-1, 2)
+        return c[:, 0] + 1j * c[:, 1]
+    return as_float_components(arr, dtype).reshape(-1)
+
+
+def f64_accumulate(op: str, x: np.ndarray, axis=None):
+    """(value, scale) of sum / sum_abs / norm2 (and their NaN-skipping forms on real data) evaluated in float64.
+    `scale` is what the rounding error of an accumulation is proportional to: the sum of magnitudes for sums,
+    the value itself for norm2."""
+    base = op[:-4] if op.endswith("_nan") else op
+    if op.endswith("_nan"):
+        x = np.where(np.isnan(x), 0, x)
+    with np.errstate(invalid="ignore", over="ignore"):
+        if base == "sum":
+            if np.iscomplexobj(x):
+                return x.sum(axis=axis), np.abs(x.real).sum(axis=axis) + np.abs(x.imag).sum(axis=axis)
+            return x.sum(axis=axis), np.abs(x).sum(axis=axis)
+        if base == "sum_abs":
+            v = np.abs(x).sum(axis=axis)
+            return v, v
+        if base == "norm2":
+            v = np.sqrt((x.real ** 2 + x.imag ** 2).sum(axis=axis)) if np.iscomplexobj(x) else np.sqrt((x * x).sum(axis=axis))
+            return v, v
+    raise KeyError(op)
+
+
+def accumulation_bound(n: int, rdtype: str, scale):
+    """Rounding-error bound of an n-term accumulation done as short sequential chains joined by a tree, in the
+    accumulator type of `rdtype`: (4 log2 n + 4) u scale with u = 2^-24 (float, and half which accumulates in
+    float) or 2^-53 (double).  (assert_accumulation adds one unit of the stored result for the half types.)
+
+    Why this bound can fail where 1e-5 sqrt(n) sum|x| cannot: take values of typical magnitude m with random
+    signs and drop k = max(1, n/100) of them.  The sum moves by about m sqrt(k); the bound is
+    (4 log2 n + 4) 2^-24 n m.  n = 7: 1 m against 6e-6 m; n = 1000: 3.2 m against 2.6e-3 m; n = 70001:
+    26 m against 0.29 m; n = 2^24: 410 m against 100 m; n = 2^26: 819 m against 432 m.  The old bound at
+    n = 70001 is 1e-5 * 265 * 70001 m = 185 m, above the shift.  For sums of one sign (sum_abs, norm2, sums of
+    squares) dropping 1 % moves the value by 1 % against a bound of 6e-6 at n = 2^26."""
+    u = 2.0 ** -53 if rdtype in ("double", "cdouble") else 2.0 ** -24
+    return (4 * np.log2(max(int(n), 2)) + 4) * u * np.asarray(scale, dtype=np.float64)
+
+
+def assert_accumulation(got, truth, n, rdtype, scale, what):
+    """|got - truth| <= accumulation_bound component-wise; equal infinities and NaN on both sides pass."""
+    g = np.asarray(got)
+    t = np.asarray(truth)
+    if np.iscomplexobj(t) or np.iscomplexobj(g):
+        g = np.stack([np.real(g), np.imag(g)], -1).astype(np.float64)
+        t = np.stack([np.real(t), np.imag(t)], -1).astype(np.float64)
+        scale = np.asarray(scale, dtype=np.float64)[..., None]
+    bound = accumulation_bound(n, rdtype, scale) + 1e-300
+    if rdtype in ("half", "chalf"):
+        bound = bound + np.abs(t) * 2.0 ** -10
+    with np.errstate(invalid="ignore"):
+        ok = (np.isnan(g) & np.isnan(t)) | (np.isinf(g) & np.isinf(t) & (np.sign(g) == np.sign(t))) | (np.abs(g - t) <= bound)
+        # a float64 evaluation that is finite where the narrower accumulator overflowed says nothing
+        ok |= np.isinf(g) & (np.abs(t) > 1e30)
+    assert np.all(ok), "%s: got %r, float64 evaluation %r, bound %r" % (what, g[~ok][:4], t[~ok][:4], np.broadcast_to(bound, g.shape)[~ok][:4])
