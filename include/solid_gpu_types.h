@@ -21,6 +21,35 @@
 #include <stdint.h>
 #include <cuda_runtime_api.h>
 
+/*
+ * Inside an Ocean build the Solid headers of the checkout are on the include
+ * path, and Ocean's own files include them before (or after) this one
+ * (include/ocean/external/ocean-solid/ocean_solid.h:20-21 pulls in solid.h).
+ * A C translation unit may define each of these anonymous struct types only
+ * once, so in that case the checkout's definitions are used -- the very
+ * headers the reference's generated solid_core_gpu.h includes
+ * (solid/src/core/gpu/solid_core_gpu.src:27-31) -- and nothing is defined here.
+ * Without them (this library's own build, bindings from other languages) the
+ * same types are defined below.  Define SOLID_B200_STANDALONE_TYPES to force
+ * the definitions below even when Solid headers can be found.
+ */
+#if !defined(SOLID_B200_STANDALONE_TYPES) && defined(__has_include)
+#  if __has_include("solid_gpu.h") && __has_include("solid/base/gpu/types_gpu.h") && \
+      __has_include("solid/core/gpu/reduce_axis.h")
+#    define SOLID_B200_USING_OCEAN_SOLID_HEADERS 1
+#  endif
+#endif
+
+#ifdef SOLID_B200_USING_OCEAN_SOLID_HEADERS
+
+#include "solid_gpu.h"                      /* solid.h: element types, solid_scalar, SD_* ; solid_gpu_properties */
+#include "solid/base/gpu/types_gpu.h"       /* solid_gpu_config                                                  */
+#include "solid/core/gpu/reduce_all.h"
+#include "solid/core/gpu/reduce_axis.h"     /* solid_gpu_reduce_axis_data, solid_gpu_reduce_axis_config          */
+#define SOLID_NUM_TYPES 15
+
+#else  /* stand-alone definitions */
+
 #ifdef __cplusplus
 #define SOLID_API extern "C"
 #else
@@ -30,6 +59,8 @@
 #define SOLID_MAX_TENSOR_DIMS 8
 #define SOLID_ERRMSG_SIZE     512
 
+typedef size_t    solid_size;
+typedef ptrdiff_t solid_index;
 typedef uint8_t   solid_bool;
 typedef uint8_t   solid_uint8;
 typedef uint16_t  solid_uint16;
@@ -125,6 +156,8 @@ typedef struct {
    int max_gridsize[3];
    int max_blocksize[3];
 } solid_gpu_properties;
+
+#endif /* stand-alone definitions */
 
 /* One operand of the mixed-dtype fused entry points (an extension; the      */
 /* reference has no counterpart because it converts every operand to a       */
