@@ -2,7 +2,7 @@
  * ABI data types of the Solid GPU function tables.
  *
  * Every structure here is laid out exactly as the Ocean tensor library
- * expects it, because the caller (Ocean's src/core/gpu/op/*.c) fills or
+ * expects it, because the caller (the files of Ocean's src/core/gpu/op) fills or
  * reads the fields directly:
  *   - element types and complex structs   solid/include/solid/base/generic/types.h:30-45
  *   - dtype index order (LUT index)       solid/include/solid/base/generic/dtype.h:23-38

@@ -6,6 +6,7 @@
 #include <cstdio>
 #include <cstdarg>
 #include <cstring>
+#include <cstdlib>
 #include <mutex>
 #include <utility>
 #include "ocean_gpu_b200.h"
@@ -60,9 +61,13 @@ int update(const OcTensorView *dst)
 }
 int finish_read(const OcTensorView *dst, const OcTensorView *src)
 {
-   // the source must not be overwritten on its own stream before this read has completed
+   // the source must not be overwritten before this read has completed: its stream waits for the
+   // destination's event, and its own event is recorded again behind that wait, so that a third stream
+   // about to write the source (which waits on the source's event) is held back as well
+   // (OcStorage_finishRead, src/base/storage.c:176-190)
    if (src->stream == dst->stream || dst->event == nullptr) return 0;
    cudaError_t st = cudaStreamWaitEvent(src->stream, dst->event, 0);
+   if (st == cudaSuccess && src->event != nullptr && src->device == dst->device) st = cudaEventRecord(src->event, src->stream);
    return st == cudaSuccess ? 0 : fail_cuda(st, "Error synchronizing streams");
 }
 
@@ -88,27 +93,56 @@ int check_elemwise(const OcTensorView *t, const char *what)
 }
 
 // ---- scratch: three round-robin slots per device (src/core/interface/storage_itf.c:61-121) ----
-struct Slot { void *ptr; size_t size; };
+// A slot is handed out again after two other requests, possibly while the kernels of its previous user are still
+// queued on some other stream.  Each slot therefore carries an event: the user records it on its stream behind its
+// last launch that touches the slot (scratch_done), and the next user's stream waits for it before it may write
+// the slot (Ocean's temporaries get the same ordering from the event of their OcStorage, src/base/storage.c:193-222).
+struct Slot { void *ptr; size_t size; cudaEvent_t done; bool recorded; };
 struct DeviceCache { Slot slot[3]; int next; };
 DeviceCache g_cache[64];
 std::mutex g_cache_lock;
 
-int temporary(int device, size_t bytes, void **out)
+// `device` must be current.  The returned slot index goes to scratch_done.
+int temporary(int device, size_t bytes, cudaStream_t stream, void **out, int *slot_index)
 {
    if (device < 0 || device >= 64) return fail("Invalid device index %d", device);
    std::lock_guard<std::mutex> guard(g_cache_lock);
    DeviceCache &c = g_cache[device];
-   Slot &s = c.slot[c.next];
+   const int k = c.next;
+   Slot &s = c.slot[k];
    c.next = (c.next + 1) % 3;
+   if (s.done == nullptr) {
+      cudaError_t st = cudaEventCreateWithFlags(&s.done, cudaEventDisableTiming);
+      if (st != cudaSuccess) { s.done = nullptr; return fail_cuda(st, "Error creating an event"); }
+   }
    if (s.size < bytes) {
-      // the slot was last handed out three requests ago; wait for the device before replacing it
-      if (s.ptr) { cudaDeviceSynchronize(); cudaFree(s.ptr); s.ptr = nullptr; s.size = 0; }
+      // replace the buffer once its last user has finished with it
+      if (s.ptr) {
+         if (s.recorded) cudaEventSynchronize(s.done);
+         cudaFree(s.ptr); s.ptr = nullptr; s.size = 0; s.recorded = false;
+      }
       size_t want = bytes < (1u << 16) ? (1u << 16) : bytes;
       cudaError_t st = cudaMalloc(&s.ptr, want);
       if (st != cudaSuccess) { s.ptr = nullptr; return fail_cuda(st, "Error allocating a temporary buffer"); }
       s.size = want;
    }
+   if (s.recorded) {
+      cudaError_t st = cudaStreamWaitEvent(stream, s.done, 0);
+      if (st != cudaSuccess) return fail_cuda(st, "Error synchronizing streams");
+   }
    *out = s.ptr;
+   *slot_index = k;
+   return 0;
+}
+
+// Everything queued on `stream` (a stream of `device`, which must be current) so far is the slot's last use.
+int scratch_done(int device, int slot_index, cudaStream_t stream)
+{
+   std::lock_guard<std::mutex> guard(g_cache_lock);
+   Slot &s = g_cache[device].slot[slot_index];
+   cudaError_t st = cudaEventRecord(s.done, stream);
+   if (st != cudaSuccess) return fail_cuda(st, "Error recording an event");
+   s.recorded = true;
    return 0;
 }
 
@@ -118,6 +152,46 @@ bool is_complex(int t) { return t >= SD_CHALF; }
 int elem_type(int t) { return is_complex(t) ? t - 3 : t; }
 int abs_type(int t) { return (t >= SD_INT8 && t <= SD_INT64) ? t - 4 : elem_type(t); }
 int sum_type(int t) { return t <= SD_UINT64 ? SD_UINT64 : (t <= SD_INT64 ? SD_INT64 : t); }
+
+
+// Operand and result types of the elementwise tables.  The Solid function is chosen by the FIRST operand's type and
+// reads and writes the others as the types listed here, so anything else would run past the end of a buffer:
+//   unary    is* -> bool, absolute -> real type of a complex source, everything else the source type
+//            (solid/src/core/gpu/template_unary.cu:176-246)
+//   binary   comparisons -> bool; shifts take an int8 count and may write the other signedness of the same width
+//            (src/core/interface/tensor_itf.c:4660-4727); power on a bool / integer base takes an int16 exponent
+//            (solid/src/core/gpu/template_binary.cu:201,260-264); everything else one type throughout
+int unary_result_type(const char *solid, int t)
+{
+   if (!strncmp(solid, "is", 2)) return SD_BOOL;
+   if (!strcmp(solid, "absolute")) return elem_type(t);
+   return t;
+}
+int check_unary_types(const char *op, const char *solid, const OcTensorView *src, const OcTensorView *dst)
+{
+   const int want = unary_result_type(solid, src->dtype);
+   if (dst->dtype != want)
+      return fail("The destination of %s on type %s must have type %s, not %s", op, dtype_names[src->dtype], dtype_names[want], dtype_names[dst->dtype]);
+   if (src->device != dst->device) return fail("All tensors of %s must be on the device of the destination", op);
+   return 0;
+}
+int check_binary_types(const char *op, const char *solid, const OcTensorView *a, const OcTensorView *b, const OcTensorView *dst)
+{
+   int want_b = a->dtype, want_dst = a->dtype;
+   bool dst_width_only = false;
+   if (!strcmp(solid, "lt") || !strcmp(solid, "le") || !strcmp(solid, "eq") || !strcmp(solid, "ne") || !strcmp(solid, "ge") || !strcmp(solid, "gt"))
+      want_dst = SD_BOOL;
+   else if (!strncmp(solid, "bitshift", 8)) { want_b = SD_INT8; dst_width_only = true; }
+   else if (!strcmp(solid, "power") && is_intlike(a->dtype)) want_b = SD_INT16;
+   if (b->dtype != want_b)
+      return fail("The second operand of %s on type %s must have type %s, not %s", op, dtype_names[a->dtype], dtype_names[want_b], dtype_names[b->dtype]);
+   const bool dst_ok = dst_width_only ? (is_intlike(dst->dtype) && solid_gpu_type_size[dst->dtype] == solid_gpu_type_size[a->dtype])
+                                      : dst->dtype == want_dst;
+   if (!dst_ok)
+      return fail("The destination of %s on type %s must have type %s, not %s", op, dtype_names[a->dtype], dtype_names[want_dst], dtype_names[dst->dtype]);
+   if (a->device != dst->device || b->device != dst->device) return fail("All tensors of %s must be on the device of the destination", op);
+   return 0;
+}
 
 } // namespace
 
@@ -155,8 +229,12 @@ extern "C" void OcFinalizeGPU_B200(void)
 {
    std::lock_guard<std::mutex> guard(g_cache_lock);
    int current = 0; cudaGetDevice(&current);
-   for (int d = 0; d < 64; d++) for (Slot &s : g_cache[d].slot) if (s.ptr) {
-      cudaSetDevice(d); cudaDeviceSynchronize(); cudaFree(s.ptr); s.ptr = nullptr; s.size = 0; }
+   for (int d = 0; d < 64; d++) for (Slot &s : g_cache[d].slot) if (s.ptr || s.done) {
+      cudaSetDevice(d);
+      if (s.recorded) cudaEventSynchronize(s.done);
+      if (s.ptr) cudaFree(s.ptr);
+      if (s.done) cudaEventDestroy(s.done);
+      s.ptr = nullptr; s.size = 0; s.done = nullptr; s.recorded = false; }
    cudaSetDevice(current);
    solid_gpu_finalize();
 }
@@ -169,6 +247,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *src, const OcTensorView *dst
    if (!same_shape(src, dst)) return fail("Tensor size mismatch in " #OP);                         \
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
    if (f == nullptr) return -1;                                                                    \
+   if (check_unary_types(#OP, #SOLID, src, dst) != 0) return -1;                                   \
    if (set_device(dst->device) != 0) return -1;                                                    \
    if (start_read(dst, src) != 0) return -1;                                                       \
    if (f(src->ndims, src->size, src->strides, src->data, dst->strides, dst->data, dst->stream) != 0) return fail_solid(); \
@@ -186,6 +265,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *src1, const OcTensorView *sr
    if (!same_shape(src1, dst) || !same_shape(src2, dst)) return fail("Tensor size mismatch in " #OP); \
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src1->dtype, #OP);                       \
    if (f == nullptr) return -1;                                                                    \
+   if (check_binary_types(#OP, #SOLID, src1, src2, dst) != 0) return -1;                           \
    if (set_device(dst->device) != 0) return -1;                                                    \
    if (start_read(dst, src1) != 0 || start_read(dst, src2) != 0) return -1;                        \
    if (f(dst->ndims, dst->size, src1->strides, src1->data, src2->strides, src2->data,              \
@@ -355,6 +435,36 @@ extern "C" int OcTensorGPU_indexToOffset(const OcTensorView *t, const solid_int6
    return finish_read(offsets, t);
 }
 
+// Two events per ordered (source device, destination device) pair, created once: `on_src` lives on the source
+// device and marks "the source stream's earlier work is done", `on_dst` on the destination device marks "the copy
+// has run".  An event can only be recorded on a stream of its own device, hence one of each.
+struct PairEvents { cudaEvent_t on_src, on_dst; bool ready; };
+static PairEvents *pair_events(int src_device, int dst_device)
+{
+   static PairEvents table[64][64];
+   static std::mutex lock;
+   if (src_device < 0 || src_device >= 64 || dst_device < 0 || dst_device >= 64) { fail("Invalid device index"); return nullptr; }
+   std::lock_guard<std::mutex> guard(lock);
+   PairEvents &p = table[src_device][dst_device];
+   if (!p.ready) {
+      int current = 0; cudaGetDevice(&current);
+      bool ok = cudaSetDevice(src_device) == cudaSuccess && cudaEventCreateWithFlags(&p.on_src, cudaEventDisableTiming) == cudaSuccess &&
+                cudaSetDevice(dst_device) == cudaSuccess && cudaEventCreateWithFlags(&p.on_dst, cudaEventDisableTiming) == cudaSuccess;
+      cudaSetDevice(current);
+      if (!ok) { (void)cudaGetLastError(); fail("Error creating an event"); return nullptr; }
+      p.ready = true;
+   }
+   return &p;
+}
+
+// OCEAN_B200_FORCE_STAGED_COPY=1 sends every cross-device copy through the dense temporaries even where peer
+// loads are possible, so that the staged path can be exercised on machines whose GPUs all see each other.
+static bool force_staged_copy()
+{
+   static const bool forced = [] { const char *e = getenv("OCEAN_B200_FORCE_STAGED_COPY"); return e && e[0] == '1'; }();
+   return forced;
+}
+
 // Can kernels on device `reader` load memory of device `owner`?  Asked of the runtime once per pair; peer access is
 // switched on at that moment (another library in the process may have done so already, which is not an error).
 static bool peer_readable(int reader, int owner)
@@ -392,43 +502,48 @@ extern "C" int OcTensorGPU_copy(const OcTensorView *src, const OcTensorView *dst
    if (src->device == dst->device) {
       if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, src->ndims, src->size, src->strides, src->data,
                             dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
-   } else if (peer_readable(dst->device, src->device)) {
+   } else if (!force_staged_copy() && peer_readable(dst->device, src->device)) {
       // other device, readable through a peer mapping (NVLink on the HGX boards): the converting copy kernel runs on
       // the destination device and loads the source over the link with plain loads -- one pass, no temporaries on
-      // either side.  The two streams belong to different devices, so they are ordered by events made here: the
-      // kernel starts after the source stream's earlier work, and the source stream continues after the kernel.
-      cudaEvent_t before, after;
+      // either side.  The two streams belong to different devices, so they are ordered by the pair's own events:
+      // the kernel starts after the source stream's earlier work, and the source stream continues after the kernel.
+      PairEvents *ev = pair_events(src->device, dst->device);
+      if (ev == nullptr) return -1;
       if (set_device(src->device) != 0) return -1;
-      if (cudaEventCreateWithFlags(&before, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
-      cudaEventRecord(before, src->stream);
-      if (set_device(dst->device) != 0) { cudaEventDestroy(before); return -1; }
-      cudaStreamWaitEvent(dst->stream, before, 0);
-      cudaEventDestroy(before);
+      cudaEventRecord(ev->on_src, src->stream);
+      if (set_device(dst->device) != 0) return -1;
+      cudaStreamWaitEvent(dst->stream, ev->on_src, 0);
       if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, src->ndims, src->size, src->strides, src->data,
                             dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
-      if (cudaEventCreateWithFlags(&after, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
-      cudaEventRecord(after, dst->stream);
-      cudaStreamWaitEvent(src->stream, after, 0);
-      cudaEventDestroy(after);
+      cudaEventRecord(ev->on_dst, dst->stream);
+      cudaStreamWaitEvent(src->stream, ev->on_dst, 0);
    } else {
       // other device without peer access: gather into a dense buffer of the source type on the source device, move it
       // with one peer copy, convert on the destination (OcTensor_intrnlCopyDevices, tensor_itf.c:895-1041)
       const size_t bytes = n1 * (size_t)solid_gpu_type_size[src->dtype];
       void *tmp_src = nullptr, *tmp_dst = nullptr;
+      int slot_src = 0, slot_dst = 0;
       size_t dense[1] = { n1 }; ptrdiff_t step[1] = { solid_gpu_type_size[src->dtype] };
-      if (set_device(src->device) != 0 || temporary(src->device, bytes, &tmp_src) != 0) return -1;
+      PairEvents *ev = pair_events(src->device, dst->device);
+      if (ev == nullptr) return -1;
+      if (set_device(src->device) != 0 || temporary(src->device, bytes, src->stream, &tmp_src, &slot_src) != 0) return -1;
       if (solid_gpu_copy_ex(src->dtype, src->dtype, 0, src->ndims, src->size, src->strides, src->data,
                             1, dense, step, tmp_src, src->stream) != 0) return fail_solid();
-      cudaEvent_t ev;
-      if (cudaEventCreateWithFlags(&ev, cudaEventDisableTiming) != cudaSuccess) return fail("Error creating an event");
-      cudaEventRecord(ev, src->stream);
-      if (set_device(dst->device) != 0 || temporary(dst->device, bytes, &tmp_dst) != 0) { cudaEventDestroy(ev); return -1; }
-      cudaStreamWaitEvent(dst->stream, ev, 0);
-      cudaEventDestroy(ev);
+      cudaEventRecord(ev->on_src, src->stream);
+      if (set_device(dst->device) != 0 || temporary(dst->device, bytes, dst->stream, &tmp_dst, &slot_dst) != 0) return -1;
+      cudaStreamWaitEvent(dst->stream, ev->on_src, 0);
       cudaError_t st = cudaMemcpyPeerAsync(tmp_dst, dst->device, tmp_src, src->device, bytes, dst->stream);
       if (st != cudaSuccess) return fail_cuda(st, "Error copying between devices");
+      // the source-side buffer is free once the transfer has run: the source stream waits for it, and the slot's
+      // event is recorded behind that wait
+      cudaEventRecord(ev->on_dst, dst->stream);
       if (solid_gpu_copy_ex(src->dtype, dst->dtype, flags, 1, dense, step, tmp_dst,
                             dst->ndims, dst->size, dst->strides, dst->data, dst->stream) != 0) return fail_solid();
+      if (scratch_done(dst->device, slot_dst, dst->stream) != 0) return -1;
+      if (set_device(src->device) != 0) return -1;
+      cudaStreamWaitEvent(src->stream, ev->on_dst, 0);
+      if (scratch_done(src->device, slot_src, src->stream) != 0) return -1;
+      if (set_device(dst->device) != 0) return -1;
    }
    if (update(dst) != 0) return -1;
    return finish_read(dst, src);
@@ -471,7 +586,7 @@ extern "C" int OcTensorGPU_maskedFill(const OcTensorView *t, const OcTensorView 
 
 // ---------------------------------------------------------------------------------- global reductions
 namespace {
-struct ReduceSetup { void *buffer; };
+struct ReduceSetup { void *buffer; int slot; };
 int reduce_begin(const OcTensorView *t, ReduceSetup *rs)             // OcTensorGPU_intrnlInitializeReduce
 {
    if (check_elemwise(t, "input") != 0) return -1;
@@ -479,7 +594,13 @@ int reduce_begin(const OcTensorView *t, ReduceSetup *rs)             // OcTensor
    size_t n = 1, bytes = 0;
    for (int i = 0; i < t->ndims; i++) n *= t->size[i];
    if (solid_gpu_reduce_all_buffer_size(n, t->device, &bytes) != 0) return fail_solid();
-   return temporary(t->device, bytes, &rs->buffer);
+   return temporary(t->device, bytes, t->stream, &rs->buffer, &rs->slot);
+}
+// the scratch is free again once everything queued on the tensor's stream so far has run
+int reduce_end(const OcTensorView *t, const ReduceSetup *rs, int status)
+{
+   if (status != 0) { fail_solid(); scratch_done(t->device, rs->slot, t->stream); return -1; }
+   return scratch_done(t->device, rs->slot, t->stream);
 }
 } // namespace
 
@@ -490,7 +611,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, int *result)             
    if (reduce_begin(t, &rs) != 0) return -1;                                                       \
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
    if (f == nullptr) return -1;                                                                    \
-   if (f(t->ndims, t->size, t->strides, t->data, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, &value, rs.buffer, t->stream)) != 0) return -1; \
    *result = value ? 1 : 0;                                                                        \
    return 0;                                                                                       \
 }
@@ -505,7 +626,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, OcScalarView *result)    
    if (f == nullptr) return -1;                                                                    \
    memset(&result->value, 0, sizeof(result->value));                                               \
    result->dtype = OcGPU_reductionResultType(#SOLID, t->dtype);                                    \
-   if (f(t->ndims, t->size, t->strides, t->data, &result->value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, &result->value, rs.buffer, t->stream)) != 0) return -1; \
    return 0;                                                                                       \
 }
 OCGPU_REDUCE_SCALAR_OPS(OCGPU_DEFINE_RSCALAR)
@@ -517,7 +638,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, solid_uint64 *result)    
    if (reduce_begin(t, &rs) != 0) return -1;                                                       \
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
    if (f == nullptr) return -1;                                                                    \
-   if (f(t->ndims, t->size, t->strides, t->data, result, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, result, rs.buffer, t->stream)) != 0) return -1; \
    return 0;                                                                                       \
 }
 OCGPU_DEFINE_RNNZ(nnz, nnz) OCGPU_DEFINE_RNNZ(nnzNaN, nnz_nan)
@@ -531,7 +652,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, double p, OcScalarView *r
    if (f == nullptr) return -1;                                                                    \
    memset(&result->value, 0, sizeof(result->value));                                               \
    result->dtype = OcGPU_reductionResultType(#SOLID, t->dtype);                                    \
-   if (f(t->ndims, t->size, t->strides, t->data, p, &result->value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, p, &result->value, rs.buffer, t->stream)) != 0) return -1; \
    return 0;                                                                                       \
 }
 OCGPU_DEFINE_RNORM(norm, norm) OCGPU_DEFINE_RNORM(normNaN, norm_nan)
@@ -545,7 +666,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, const OcScalarView *bound
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
    if (f == nullptr) return -1;                                                                    \
    solid_scalar b = bound->value;                                                                  \
-   if (f(t->ndims, t->size, t->strides, t->data, &b, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, &b, &value, rs.buffer, t->stream)) != 0) return -1; \
    *result = value ? 1 : 0;                                                                        \
    return 0;                                                                                       \
 }
@@ -561,7 +682,7 @@ extern "C" int OcTensorGPU_##OP(const OcTensorView *t, const OcScalarView *lower
    solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, t->dtype, #OP);                          \
    if (f == nullptr) return -1;                                                                    \
    solid_scalar lo = lower->value, hi = upper->value;                                              \
-   if (f(t->ndims, t->size, t->strides, t->data, &lo, &hi, &value, rs.buffer, t->stream) != 0) return fail_solid(); \
+   if (reduce_end(t, &rs, f(t->ndims, t->size, t->strides, t->data, &lo, &hi, &value, rs.buffer, t->stream)) != 0) return -1; \
    *result = value ? 1 : 0;                                                                        \
    return 0;                                                                                       \
 }
@@ -573,8 +694,9 @@ namespace {
 // Split src into kept and reduced dimensions, plan, fetch scratch (OcTensorGPU_intrnlAxisReduce,
 // tensor_reduce_axis_gpu.c:127-158).
 int axis_begin(const OcTensorView *src, int n, const int *axes, const OcTensorView *dst, const char *solid_name,
-               solid_gpu_reduce_axis_config *config)
+               solid_gpu_reduce_axis_config *config, int *slot)
 {
+   *slot = -1;
    if (check_elemwise(src, "source") != 0 || check_elemwise(dst, "destination") != 0) return -1;
    bool reduced[SOLID_MAX_TENSOR_DIMS] = { false };
    for (int i = 0; i < n; i++) {
@@ -606,35 +728,39 @@ int axis_begin(const OcTensorView *src, int n, const int *axes, const OcTensorVi
                                      rd, rsize, rst, dst->stream) != 0) return fail_solid();
    if (config->bufferSize > 0) {
       void *buf = nullptr;
-      if (temporary(dst->device, config->bufferSize, &buf) != 0) return -1;
+      if (temporary(dst->device, config->bufferSize, dst->stream, &buf, slot) != 0) return -1;
       config->data.ptrBuffer = (char *)buf;
    }
    return start_read(dst, src);
+}
+int axis_end(const OcTensorView *src, const OcTensorView *dst, int slot, int status)
+{
+   if (status != 0) fail_solid();
+   if (slot >= 0 && scratch_done(dst->device, slot, dst->stream) != 0) return -1;
+   if (status != 0) return -1;
+   if (update(dst) != 0) return -1;
+   return finish_read(dst, src);
 }
 } // namespace
 
 #define OCGPU_DEFINE_AXIS(OP, SOLID)                                                               \
 extern "C" int OcTensorGPU_##OP(const OcTensorView *src, int n, const int *axes, const OcTensorView *dst) \
 {                                                                                                  \
-   solid_gpu_reduce_axis_config config;                                                            \
-   if (axis_begin(src, n, axes, dst, #SOLID, &config) != 0) return -1;                             \
-   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   solid_gpu_reduce_axis_config config; int slot;                                                  \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src ? src->dtype : -1, #OP);             \
    if (f == nullptr) return -1;                                                                    \
-   if (f(&config) != 0) return fail_solid();                                                       \
-   if (update(dst) != 0) return -1;                                                                \
-   return finish_read(dst, src);                                                                   \
+   if (axis_begin(src, n, axes, dst, #SOLID, &config, &slot) != 0) return -1;                      \
+   return axis_end(src, dst, slot, f(&config));                                                    \
 }
 OCGPU_AXIS_OPS(OCGPU_DEFINE_AXIS)
 
 #define OCGPU_DEFINE_AXIS_NORM(OP, SOLID)                                                          \
 extern "C" int OcTensorGPU_##OP(const OcTensorView *src, double p, int n, const int *axes, const OcTensorView *dst) \
 {                                                                                                  \
-   solid_gpu_reduce_axis_config config;                                                            \
-   if (axis_begin(src, n, axes, dst, #SOLID, &config) != 0) return -1;                             \
-   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src->dtype, #OP);                        \
+   solid_gpu_reduce_axis_config config; int slot;                                                  \
+   solid_funptr_gpu_##SOLID f = lookup(solid_gpu_##SOLID, src ? src->dtype : -1, #OP);             \
    if (f == nullptr) return -1;                                                                    \
-   if (f(&config, p) != 0) return fail_solid();                                                    \
-   if (update(dst) != 0) return -1;                                                                \
-   return finish_read(dst, src);                                                                   \
+   if (axis_begin(src, n, axes, dst, #SOLID, &config, &slot) != 0) return -1;                      \
+   return axis_end(src, dst, slot, f(&config, p));                                                 \
 }
 OCGPU_DEFINE_AXIS_NORM(axisNorm, axis_norm) OCGPU_DEFINE_AXIS_NORM(axisNormNaN, axis_norm_nan)

@@ -94,6 +94,32 @@ def test_errors_before_any_cuda_call():
     with pytest.raises(OceanError, match="data type of the tensor"):
         sv = oc.scalar(b"\0" * 8, "double")
         oc._check(oc.fn("fill")(C.byref(a), C.byref(sv)), "fill")
+    # operand and result types: the kernel is chosen by the first operand and would read or write the others as
+    # the types it expects, past the end of a narrower buffer
+    with pytest.raises(OceanError, match="destination of sqrt on type float must have type float, not int8"):
+        oc._check(oc.fn("sqrt")(C.byref(a), C.byref(fake_view("int8"))), "sqrt")
+    with pytest.raises(OceanError, match="must have type bool, not float"):
+        oc._check(oc.fn("isnan")(C.byref(a), C.byref(d)), "isnan")
+    with pytest.raises(OceanError, match="must have type double, not complex-double"):
+        vc = fake_view("cdouble")
+        oc._check(oc.fn("absolute")(C.byref(vc), C.byref(vc)), "absolute")
+    with pytest.raises(OceanError, match="second operand of add on type float must have type float, not double"):
+        oc._check(oc.fn("add")(C.byref(a), C.byref(fake_view("double")), C.byref(d)), "add")
+    with pytest.raises(OceanError, match="destination of add on type float must have type float, not half"):
+        oc._check(oc.fn("add")(C.byref(a), C.byref(b), C.byref(fake_view("half"))), "add")
+    with pytest.raises(OceanError, match="must have type bool, not float"):
+        oc._check(oc.fn("elemwiseLT")(C.byref(a), C.byref(b), C.byref(d)), "elemwiseLT")
+    i32, u32 = fake_view("int32"), fake_view("uint32")
+    with pytest.raises(OceanError, match="second operand of bitshiftLeft on type int32 must have type int8"):
+        oc._check(oc.fn("bitshiftLeft")(C.byref(i32), C.byref(i32), C.byref(i32)), "bitshiftLeft")
+    with pytest.raises(OceanError, match="destination of bitshiftLeft"):
+        oc._check(oc.fn("bitshiftLeft")(C.byref(i32), C.byref(fake_view("int8")), C.byref(fake_view("int16"))), "bitshiftLeft")
+    with pytest.raises(OceanError, match="second operand of power on type int32 must have type int16"):
+        oc._check(oc.fn("power")(C.byref(i32), C.byref(i32), C.byref(i32)), "power")
+    with pytest.raises(OceanError, match="on the device of the destination"):
+        oc._check(oc.fn("add")(C.byref(a), C.byref(fake_view("float", device=1)), C.byref(d)), "add")
+    with pytest.raises(OceanError, match="on the device of the destination"):
+        oc._check(oc.fn("negative")(C.byref(fake_view("float", device=1)), C.byref(d)), "negative")
 
 
 # ------------------------------------------------------------------------------------ GPU
@@ -240,6 +266,55 @@ def test_stream_protocol_orders_producer_and_consumer(gpu):
     got = c.storage[: 4 * n].cpu().numpy().view(np.float32)
     assert np.all(got == 3.0)
     torch.cuda.synchronize()
+
+
+@pytest.mark.gpu
+def test_scratch_slots_are_ordered_across_streams(gpu):
+    """Split axis reductions take their partial-result buffer from a three-slot cache per device, so the fourth
+    request reuses the first slot.  Six such reductions alternate over two streams, the first stream held back by
+    a long idle kernel: without an event per slot the later calls on the free stream would overwrite partials that
+    the held-back calls have not folded yet."""
+    import torch
+    from solid_b200 import Tensor
+    oc = _ocean.get()
+    rng = np.random.default_rng(12)
+    rows, cols = 64, 1 << 15                                   # few outputs, long strided range: split over blocks
+    hosts = [rng.integers(-1000, 1000, (rows, cols)).astype(np.int32) for _ in range(6)]
+    srcs = [Tensor.from_numpy(np.asfortranarray(h)) for h in hosts]
+    outs = [Tensor.empty([rows], "int64") for _ in range(6)]
+    streams = [torch.cuda.Stream(), torch.cuda.Stream()]
+    events = [torch.cuda.Event(), torch.cuda.Event()]
+    for st, ev in zip(streams, events):
+        with torch.cuda.stream(st):
+            ev.record()
+    torch.cuda.synchronize()
+    axes = (C.c_int * 1)(1)
+    with torch.cuda.stream(streams[0]):
+        torch.cuda._sleep(int(4e8))                            # roughly 0.2 s before stream 0 may start
+    for k in range(6):
+        st, ev = streams[k % 2], events[k % 2]
+        vs, vd = oc.view(srcs[k], st.cuda_stream, ev.cuda_event), oc.view(outs[k], st.cuda_stream, ev.cuda_event)
+        oc._check(oc.fn("axisSum")(C.byref(vs), C.c_int(1), axes, C.byref(vd)), "axisSum")
+    torch.cuda.synchronize()
+    for k in range(6):
+        assert np.array_equal(outs[k].numpy(), hosts[k].astype(np.int64).sum(axis=1)), k
+
+
+@pytest.mark.gpu
+def test_copy_between_devices_through_dense_temporaries(gpu):
+    """The staged path (dense temporary on each device and one peer copy) is what runs where a device cannot load
+    a peer's memory; on machines whose GPUs all see each other it is reached by OCEAN_B200_FORCE_STAGED_COPY=1,
+    which the library reads once, hence the child process."""
+    import os
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    env = dict(os.environ, OCEAN_B200_FORCE_STAGED_COPY="1")
+    res = subprocess.run([sys.executable, "-m", "pytest", "-q", "-x", "-m", "gpu",
+                          "%s::test_copy_between_devices" % Path(__file__).resolve()],
+                         env=env, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, cwd=str(ROOT))
+    assert res.returncode == 0 and "1 passed" in res.stdout, res.stdout[-2000:]
 
 
 @pytest.mark.gpu

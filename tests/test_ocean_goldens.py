@@ -1,0 +1,286 @@
+"""The reference's own callers and its own golden scripts on top of this repository's libraries.
+
+CPU tier (needs the reference checkout, found through $OCEAN_REFERENCE_DIR or as a directory `reference` beside
+this repository; skipped without it):
+  * every function and table that the header generated from the reference's solid_core_gpu.src declares is
+    declared here with the same signature, and is exported;
+  * the nine files of the reference's src/core/gpu/op compile against include/solid_core_gpu.h;
+  * the Ocean stack built by oracle/build_ocean.py (the reference's unchanged C library, GPU module and Python
+    binding, linked against libsolid_core_gpu.so) imports and computes on the CPU device.
+
+GPU tier (needs only what oracle/build_ocean.py left under oracle/_ref/ocean, which travels with the repository):
+  * the reference's GPU golden scripts, examples/python/gpu/{tensors,index}/NAME.py, print exactly NAME.ref
+    - with the reference's UNCHANGED GPU module (its own dispatch files) over this Solid library, and
+    - with this repository's dispatch registered in OcModuleCore (csrc/ocean_module.c + libocean_gpu_b200.so);
+  * the reference's CPU golden scripts examples/python/cpu/tensors/NAME.py, re-targeted to ocean.gpu[0], print
+    NAME.ref with the device name replaced: the whole interface layer (promotion, broadcasting, byte order,
+    temporaries, in-place forms) then runs on these kernels.
+"""
+from __future__ import annotations
+
+import os
+import re
+import subprocess
+import sys
+import tempfile
+from concurrent.futures import ThreadPoolExecutor
+from pathlib import Path
+
+import pytest
+
+ROOT = Path(__file__).resolve().parent.parent
+OCEAN = ROOT / "oracle" / "_ref" / "ocean"
+CUDA_INC = Path(os.environ.get("CUDA_HOME", "/usr/local/cuda")) / "include"
+
+
+def reference_dir():
+    cands = [os.environ.get("OCEAN_REFERENCE_DIR"), str(ROOT.parent / "reference")]
+    for c in cands:
+        if c and (Path(c) / "solid" / "bin" / "generate.py").exists():
+            return Path(c)
+    return None
+
+
+needs_reference = pytest.mark.skipif(reference_dir() is None, reason="no reference checkout")
+needs_stack = pytest.mark.skipif(not (OCEAN / "python" / "ocean.py").exists(), reason="oracle/build_ocean.py has not run")
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# CPU tier: the header against the reference's generated one
+# ---------------------------------------------------------------------------------------------------------------
+def _strip_param_name(p: str) -> str:
+    p = p.strip()
+    m = re.match(r"^(.*?[\s\*])([A-Za-z_]\w*)$", p)
+    if m and m.group(1).strip() and m.group(2) not in ("void", "int", "char", "double", "size_t", "ptrdiff_t"):
+        p = m.group(1)
+    return re.sub(r"\s+", " ", p.replace("*", " * ")).strip()
+
+
+def _declarations(text: str):
+    """name -> normalised signature for functions, name -> (typedef name, dimensions) for tables."""
+    text = re.sub(r"\s+", " ", text)
+    funcs, tables = {}, {}
+    for m in re.finditer(r"\b(int|void|solid_gpu_properties \*)\s*(solid_gpu_\w+)\s*\(([^()]*)\)\s*;", text):
+        ret, name, params = m.groups()
+        funcs[name] = ret.strip() + "(" + ", ".join(_strip_param_name(p) for p in params.split(",")) + ")"
+    for m in re.finditer(r"\b(solid_funptr_gpu_\w+)\s+(solid_gpu_\w+)((?:\s*\[[^\]]*\])+)\s*;", text):
+        tables[m.group(2)] = (m.group(1), re.sub(r"\s+", "", m.group(3)).replace("SOLID_NUM_TYPES", "15"))
+    typedefs = {}
+    for m in re.finditer(r"typedef int \(\*(solid_funptr_gpu_\w+)\)\s*\(([^()]*)\)\s*;", text):
+        typedefs[m.group(1)] = ", ".join(_strip_param_name(p) for p in m.group(2).split(","))
+    return funcs, tables, typedefs
+
+
+def _preprocess(header: Path, includes, defines=()):
+    cmd = ["gcc", "-E", "-P", *["-D" + d for d in defines], *["-I%s" % i for i in includes], str(header)]
+    res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.PIPE, text=True)
+    assert res.returncode == 0, res.stderr[-2000:]
+    return res.stdout
+
+
+@needs_reference
+def test_every_reference_declaration_has_an_identical_counterpart(tmp_path):
+    ref = reference_dir()
+    gen = subprocess.run([sys.executable, str(ref / "solid/bin/generate.py"), "-h",
+                          str(ref / "solid/src/core/gpu/solid_core_gpu.src"), str(tmp_path)],
+                         stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert gen.returncode == 0 and (tmp_path / "solid_core_gpu.h").exists(), gen.stdout[-1500:]
+    theirs = _preprocess(tmp_path / "solid_core_gpu.h", [ref / "solid/include", CUDA_INC])
+    ours = _preprocess(ROOT / "include" / "solid_core_gpu.h", [ROOT / "include", CUDA_INC], ["SOLID_B200_STANDALONE_TYPES"])
+    rf, rt, rd = _declarations(theirs)
+    of, ot, od = _declarations(ours)
+    assert len(rf) > 2000 and len(rt) > 120, (len(rf), len(rt))
+    # declared by the reference but defined nowhere in it (solid_core_gpu.src:290); nothing can call it
+    rf.pop("solid_gpu_reduce_get_buffer_size", None)
+    # helpers of the reference's own kernel generators (launch analysis), not part of what Ocean binds
+    internal = {n for n in rf if re.search(r"_analyze$|_large_indexing$|reduce_all_config$|reduce_axis_(thread|warp|block)", n)}
+    missing = sorted(n for n in rf if n not in of and n not in internal)
+    assert not missing, "not declared here: %s" % missing[:20]
+    different = sorted(n for n in rf if n in of and rf[n] != of[n])
+    assert not different, [(n, rf[n], of[n]) for n in different[:5]]
+    assert not sorted(n for n in rt if n not in ot), "tables not declared here"
+    bad_tables = sorted(n for n in rt if rt[n] != ot[n])
+    assert not bad_tables, [(n, rt[n], ot[n]) for n in bad_tables[:5]]
+    bad_types = sorted(n for n in rd if n not in od or rd[n] != od[n])
+    assert not bad_types, [(n, rd[n], od.get(n)) for n in bad_types[:5]]
+    # and the library exports every one of them
+    import ctypes
+    dll = ctypes.CDLL(str(ROOT / "ocean-tensor-package_b200" / "lib" / "libsolid_core_gpu.so"))
+    unexported = sorted(n for n in list(rf) + list(rt) if n not in internal and not hasattr(dll, n))
+    assert not unexported, unexported[:20]
+
+
+@needs_reference
+def test_abi_structures_have_the_reference_layout(tmp_path):
+    """The stand-alone type definitions against the reference's: same sizes and field offsets."""
+    ref = reference_dir()
+    prog = r'''
+#include <stdio.h>
+#include <stddef.h>
+#include "solid_core_gpu.h"
+#define F(T, M) printf(#T "." #M " %zu %zu\n", offsetof(T, M), sizeof(((T *)0)->M));
+int main(void)
+{  printf("scalar %zu config %zu axis %zu data %zu props %zu\n", sizeof(solid_scalar), sizeof(solid_gpu_config),
+          sizeof(solid_gpu_reduce_axis_config), sizeof(solid_gpu_reduce_axis_data), sizeof(solid_gpu_properties));
+   F(solid_gpu_reduce_axis_data, size) F(solid_gpu_reduce_axis_data, rsize) F(solid_gpu_reduce_axis_data, strides1)
+   F(solid_gpu_reduce_axis_data, strides2) F(solid_gpu_reduce_axis_data, rstrides) F(solid_gpu_reduce_axis_data, ptr1)
+   F(solid_gpu_reduce_axis_data, ptr2) F(solid_gpu_reduce_axis_data, ptrBuffer) F(solid_gpu_reduce_axis_data, nelem)
+   F(solid_gpu_reduce_axis_data, relem) F(solid_gpu_reduce_axis_data, ndims) F(solid_gpu_reduce_axis_data, rdims)
+   F(solid_gpu_reduce_axis_config, data) F(solid_gpu_reduce_axis_config, mode) F(solid_gpu_reduce_axis_config, gridSize)
+   F(solid_gpu_reduce_axis_config, blockSize) F(solid_gpu_reduce_axis_config, gridSizeFinalize)
+   F(solid_gpu_reduce_axis_config, blockSizeFinalize) F(solid_gpu_reduce_axis_config, bufferSize)
+   F(solid_gpu_reduce_axis_config, sharedMem) F(solid_gpu_reduce_axis_config, sharedMemFinalize) F(solid_gpu_reduce_axis_config, stream)
+   F(solid_gpu_properties, major) F(solid_gpu_properties, multiprocessor_count) F(solid_gpu_properties, max_resident_blocks_per_device)
+   F(solid_gpu_properties, max_shared_mem_per_threadblock) F(solid_gpu_properties, max_gridsize) F(solid_gpu_properties, max_blocksize)
+   F(solid_scalar, _cdouble) F(solid_scalar, _half) F(solid_gpu_gemm_plan, M) F(solid_gpu_gemm_plan, gridsize) F(solid_gpu_gemm_plan, sharedmem)
+   printf("enum %d %d %d\n", (int)SD_BOOL, (int)SD_HALF, (int)SD_CDOUBLE);
+   return 0;
+}
+'''
+    src = tmp_path / "layout.c"
+    src.write_text(prog)
+    outs = []
+    for tag, flags in (("alone", ["-DSOLID_B200_STANDALONE_TYPES", "-I%s" % (ROOT / "include")]),
+                       ("ocean", ["-I%s" % (ROOT / "include"), "-I%s" % (ref / "solid/include")])):
+        exe = tmp_path / ("layout_" + tag)
+        res = subprocess.run(["gcc", "-std=gnu99", *flags, "-I%s" % CUDA_INC, str(src), "-o", str(exe)],
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        assert res.returncode == 0, res.stdout[-2000:]
+        outs.append(subprocess.run([str(exe)], stdout=subprocess.PIPE, text=True).stdout)
+    assert outs[0] == outs[1] and "enum 0 9 14" in outs[0], outs
+
+
+@needs_reference
+def test_reference_dispatch_files_compile_against_this_header():
+    """src/core/gpu/op of the reference, unchanged, with include/ of this repository first on the include path, and
+    this header in either order relative to the reference's solid.h."""
+    ref = reference_dir()
+    inc = ["-I%s" % (ROOT / "include"), "-I%s" % (ref / "include"), "-I%s" % (ref / "solid/include"), "-I%s" % CUDA_INC]
+    files = sorted((ref / "src/core/gpu/op").glob("tensor_*_gpu.c"))
+    assert len(files) == 9, files
+    for f in files:
+        res = subprocess.run(["gcc", "-std=gnu99", "-fsyntax-only", "-Wno-implicit-function-declaration", *inc, str(f)],
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        assert res.returncode == 0, "%s\n%s" % (f.name, res.stdout[-1500:])
+    for order in (('"ocean/external/ocean-solid/ocean_solid.h"', '"solid_core_gpu.h"'),
+                  ('"solid_core_gpu.h"', '"ocean/external/ocean-solid/ocean_solid.h"')):
+        code = "".join("#include %s\n" % h for h in order) + "int f(void) { return solid_gpu_add[SD_FLOAT] != 0; }\n"
+        res = subprocess.run(["gcc", "-std=gnu99", "-fsyntax-only", "-x", "c", *inc, "-"], input=code,
+                             stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        assert res.returncode == 0, "%s\n%s" % (order, res.stdout[-1500:])
+
+
+# ---------------------------------------------------------------------------------------------------------------
+# running golden scripts
+# ---------------------------------------------------------------------------------------------------------------
+def _env(variant: str):
+    env = dict(os.environ, PYTHONPATH=str(OCEAN / "python"))
+    if variant == "b200":                                     # this repository's dispatch: lib_b200/libocean_gpu.so first
+        env["LD_LIBRARY_PATH"] = str(OCEAN / "lib_b200") + ":" + env.get("LD_LIBRARY_PATH", "")
+    return env
+
+
+def _run_script(path: Path, cwd: Path, env):
+    res = subprocess.run([sys.executable, str(path)], cwd=str(cwd), env=env, stdout=subprocess.PIPE,
+                         stderr=subprocess.STDOUT, text=True, timeout=600)
+    return res.stdout
+
+
+@needs_stack
+def test_ocean_stack_runs_on_the_cpu_device():
+    """The binding built over this repository's Solid GPU library loads without a GPU and computes on the CPU
+    device (the GPU module then registers no device), and a few of the reference's CPU goldens print their .ref."""
+    out = subprocess.run([sys.executable, "-c",
+                          "import ocean\na = ocean.asTensor([1,2,3], ocean.float)\nprint(ocean.sum(a + a))"],
+                         env=_env("reference"), stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+    assert out.stdout.strip() == "12", out.stdout
+    ex = OCEAN / "examples" / "cpu" / "tensors"
+    for name in ("tensor_add_01", "tensor_copy_03", "ocean_sum_01", "ocean_axis_reduce_01", "ocean_unary_01"):
+        assert _run_script(ex / (name + ".py"), ex, _env("reference")) == (ex / (name + ".ref")).read_text(), name
+
+
+GPU_SCRIPTS = sorted(p.relative_to(OCEAN / "examples") for p in (OCEAN / "examples" / "gpu").rglob("*.py")) \
+    if (OCEAN / "examples" / "gpu").exists() else []
+CPU_SCRIPTS = sorted(p.relative_to(OCEAN / "examples") for p in (OCEAN / "examples" / "cpu" / "tensors").glob("*.py")) \
+    if (OCEAN / "examples" / "cpu").exists() else []
+
+# Scripts that place tensors on a second GPU
+TWO_GPUS = {"tensor_copy_09", "tensor_device_cast_01"}
+# gpu/tensors/tensor_fillnan_01.ref was recorded from the reference's GPU kernels, whose fill_nan launches the plain
+# fill kernel (solid/src/core/gpu/template_fill.cu:72-79) and so overwrites every element.  The reference's CPU code,
+# which is the oracle here, replaces only the NaNs; the CPU golden of the same script says what that prints.
+CPU_REF_INSTEAD = {"tensor_fillnan_01"}
+
+# cpu/tensors scripts whose .ref cannot be reproduced on ocean.gpu[0] for reasons outside these kernels
+RETARGET_EXCLUDED = {
+    # Python-2 era artefacts in the .ref files themselves (they fail on the reference's own CPU device too)
+    "ocean_astensor_03": "py2 repr in .ref", "ocean_astensor_06": "py2 repr in .ref", "ocean_cast_05": "py2 repr in .ref",
+    "ocean_divide_01": "py2 integer division in the script", "ocean_norm_01": "py2 artefact in .ref",
+}
+
+
+def _retargeted(script: Path, tmp: Path) -> Path:
+    text = script.read_text().replace("import pyOcean_cpu as ocean",
+                                      "import ocean\nocean.setDefaultDevice(ocean.gpu[0])")
+    out = tmp / script.name
+    out.write_text(text)
+    return out
+
+
+@pytest.fixture(scope="module")
+def golden_outputs():
+    """Every script once per variant, eight at a time; {(variant, relative path): stdout}."""
+    import torch
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    if not (OCEAN / "python" / "ocean.py").exists():
+        pytest.skip("oracle/build_ocean.py has not run")
+    ngpu = torch.cuda.device_count()
+    tmp = Path(tempfile.mkdtemp(prefix="ocean_goldens_"))
+    jobs = []
+    for variant in ("reference", "b200"):
+        for rel in GPU_SCRIPTS:
+            if rel.stem in TWO_GPUS and ngpu < 2:
+                continue
+            src = OCEAN / "examples" / rel
+            jobs.append(((variant, str(rel)), src, src.parent, _env(variant)))
+        for rel in CPU_SCRIPTS:
+            if rel.stem in RETARGET_EXCLUDED:
+                continue
+            d = tmp / variant
+            d.mkdir(exist_ok=True)
+            jobs.append(((variant, str(rel)), _retargeted(OCEAN / "examples" / rel, d), d, _env(variant)))
+    with ThreadPoolExecutor(8) as pool:
+        outs = list(pool.map(lambda j: _run_script(j[1], j[2], j[3]), jobs))
+    return {j[0]: o for j, o in zip(jobs, outs)}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("variant", ["reference", "b200"])
+@pytest.mark.parametrize("rel", GPU_SCRIPTS, ids=[str(r) for r in GPU_SCRIPTS])
+def test_reference_gpu_golden(rel, variant, golden_outputs):
+    key = (variant, str(rel))
+    if key not in golden_outputs:
+        pytest.skip("needs two GPUs")
+    ref = OCEAN / "examples" / rel.with_suffix(".ref")
+    want = ref.read_text()
+    if rel.stem in CPU_REF_INSTEAD:
+        want = (OCEAN / "examples" / "cpu" / "tensors" / (rel.stem + ".ref")).read_text().replace(" on cpu>", " on gpu0>")
+    assert golden_outputs[key] == want
+
+
+# Differences between a CPU golden and its run on ocean.gpu[0] that do not come from these kernels; each entry says
+# what differs.  Filled in from the first GPU run; everything not listed must print its .ref exactly.
+RETARGET_KNOWN = {}
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("variant", ["reference", "b200"])
+@pytest.mark.parametrize("rel", CPU_SCRIPTS, ids=[str(r) for r in CPU_SCRIPTS])
+def test_reference_cpu_golden_on_gpu(rel, variant, golden_outputs):
+    if rel.stem in RETARGET_EXCLUDED:
+        pytest.skip(RETARGET_EXCLUDED[rel.stem])
+    if (rel.stem, variant) in RETARGET_KNOWN or (rel.stem, "both") in RETARGET_KNOWN:
+        pytest.skip(RETARGET_KNOWN.get((rel.stem, variant)) or RETARGET_KNOWN[(rel.stem, "both")])
+    want = (OCEAN / "examples" / rel.with_suffix(".ref")).read_text().replace(" on cpu>", " on gpu0>")
+    assert golden_outputs[(variant, str(rel))] == want
