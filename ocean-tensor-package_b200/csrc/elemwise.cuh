@@ -10,6 +10,9 @@
 //               scalar): each thread moves VEC elements per operand with 128-bit
 //               ld.global.cs / st.global.cs, UNROLL independent vectors in flight,
 //               64-bit element counts (2^32 elements and beyond);
+//   ew_tiled    a source is dense along another dimension than the destination
+//               (transposed views): 32 x 32 tiles staged through shared memory, so
+//               both sides are accessed along their dense dimension;
 //   ew_strided  general case: the innermost dimension is vectorised when every
 //               operand is dense or broadcast along it and rows start on 16-byte
 //               boundaries (VEC > 1), otherwise one element per access (VEC == 1);
@@ -271,6 +274,143 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
    }
 }
 
+
+// ---------------------------------------------------------------------------
+// ew_tiled: some source is dense along ANOTHER dimension T than the destination (a transposed view, the classic
+// B = A^T or C = A^T + B).  Read along the destination's dense dimension, such a source touches one element per
+// 32-byte sector, which is what ew_strided<VEC = 1> (and the reference's kernels) do.  Here a block owns a
+// 32 x 32 tile over (dimension 0, dimension T): sources dense along T are read row by row along T (coalesced),
+// parked in shared memory (row pitch 33 elements, so the transposed read is free of bank conflicts for 4-byte
+// elements and two-way at most for wider ones), and the block then walks the tile along dimension 0, taking
+// those sources from shared memory and everything else (destination, sources dense or broadcast along
+// dimension 0) straight from global memory.  Every byte still moves once.  Remaining dimensions are decomposed
+// once per block.
+// ---------------------------------------------------------------------------
+constexpr int EW_TILE = 32;
+
+template <int NOPS> struct EwTiledParams {
+   char    *ptr[NOPS];
+   int64_t  stride[NOPS][MAXD];
+   uint32_t size[MAXD];
+   FastDiv  div[MAXD];
+   FastDiv  div_tiles0, div_tilesT;
+   uint32_t tiles0, tilesT;
+   int      ndims, tdim;
+   uint32_t staged;                  // bit k: source k goes through shared memory
+};
+
+template <class A>
+__global__ void __launch_bounds__(EW_THREADS) ew_tiled(const A apply, const EwTiledParams<A::NIN + 1> p)
+{
+   using X = ew_traits<A>;
+   constexpr int NIN = X::NIN, NOPS = NIN + 1, TS = EW_TILE, ROWS = EW_THREADS / TS, PER = TS / ROWS;
+   using out_t = typename X::out_t; using in1_t = typename X::in1_t; using in2_t = typename X::in2_t;
+   __shared__ in1_t tile1[NIN >= 1 ? TS : 1][NIN >= 1 ? TS + 1 : 1];
+   __shared__ in2_t tile2[NIN >= 2 ? TS : 1][NIN >= 2 ? TS + 1 : 1];
+   const uint32_t tx = threadIdx.x % TS, ty = threadIdx.x / TS;
+   const int T = p.tdim;
+
+   // block -> (tile along 0, tile along T, position in the remaining dimensions)
+   uint32_t q = blockIdx.x;
+   uint32_t qq = fastdiv(q, p.div_tiles0);
+   const uint32_t base0 = (q - qq * p.tiles0) * TS; q = qq;
+   qq = fastdiv(q, p.div_tilesT);
+   const uint32_t baseT = (q - qq * p.tilesT) * TS; q = qq;
+   int64_t off[NOPS];
+#pragma unroll
+   for (int k = 0; k < NOPS; k++) off[k] = 0;
+   for (int d = 1; d < p.ndims; d++) {
+      if (d == T) continue;
+      qq = fastdiv(q, p.div[d]);
+      const uint32_t c = q - qq * p.size[d]; q = qq;
+#pragma unroll
+      for (int k = 0; k < NOPS; k++) off[k] += (int64_t)c * p.stride[k][d];
+   }
+   const uint32_t size0 = p.size[0], sizeT = p.size[T];
+
+   // park the sources that are dense along T: thread (tx, ty) reads positions (ty + ROWS j) along 0, tx along T
+   if (p.staged) {
+      in1_t r1[PER]; in2_t r2[PER];
+      const uint32_t iT = baseT + tx;
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+         const uint32_t i0 = base0 + ty + ROWS * j;
+         if (i0 < size0 && iT < sizeT) {
+            if constexpr (NIN >= 1) if (p.staged & 1u) r1[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)i0 * p.stride[0][0] + (int64_t)iT * p.stride[0][T]);
+            if constexpr (NIN >= 2) if (p.staged & 2u) r2[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)i0 * p.stride[1][0] + (int64_t)iT * p.stride[1][T]);
+         }
+      }
+#pragma unroll
+      for (int j = 0; j < PER; j++) {
+         if constexpr (NIN >= 1) if (p.staged & 1u) tile1[ty + ROWS * j][tx] = r1[j];
+         if constexpr (NIN >= 2) if (p.staged & 2u) tile2[ty + ROWS * j][tx] = r2[j];
+      }
+      __syncthreads();
+   }
+
+   // walk the tile along dimension 0: thread (tx, ty) handles positions tx along 0, (ty + ROWS j) along T
+   const uint32_t i0 = base0 + tx;
+   in1_t a[PER]; in2_t b[PER];
+#pragma unroll
+   for (int j = 0; j < PER; j++) {
+      const uint32_t iT = baseT + ty + ROWS * j;
+      if (i0 < size0 && iT < sizeT) {
+         if constexpr (NIN >= 1) {
+            if (p.staged & 1u) a[j] = tile1[tx][ty + ROWS * j];
+            else a[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)i0 * p.stride[0][0] + (int64_t)iT * p.stride[0][T]);
+         }
+         if constexpr (NIN >= 2) {
+            if (p.staged & 2u) b[j] = tile2[tx][ty + ROWS * j];
+            else b[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)i0 * p.stride[1][0] + (int64_t)iT * p.stride[1][T]);
+         }
+      }
+   }
+#pragma unroll
+   for (int j = 0; j < PER; j++) {
+      const uint32_t iT = baseT + ty + ROWS * j;
+      if (i0 < size0 && iT < sizeT)
+         st_one<out_t>(p.ptr[NIN] + off[NIN] + (int64_t)i0 * p.stride[NIN][0] + (int64_t)iT * p.stride[NIN][T], apply(a[j], b[j]));
+   }
+}
+
+// Can the operation run as ew_tiled?  Requires aligned elements, a destination dense along dimension 0, at least
+// one source that is neither dense nor constant along dimension 0 but dense along some other dimension, that
+// dimension being the same for all such sources, and tiles worth the trouble.  Fills the parameters if so.
+template <class A>
+bool ew_plan_tiled(const Layout<A::NIN + 1> &L, EwTiledParams<A::NIN + 1> &p)
+{
+   using X = ew_traits<A>;
+   constexpr int NIN = X::NIN, NOPS = NIN + 1;
+   const int esize[3] = { NIN >= 1 ? X::s_in1 : X::s_out, NIN >= 2 ? X::s_in2 : X::s_out, X::s_out };
+   auto es = [&](int k) { return k == NIN ? X::s_out : esize[k]; };
+   if (NIN == 0 || L.ndims < 2 || L.stride[NIN][0] != es(NIN)) return false;
+   int tdim = -1; uint32_t staged = 0;
+   for (int k = 0; k < NIN; k++) {
+      if (L.stride[k][0] == es(k) || L.stride[k][0] == 0) continue;
+      int mine = -1;
+      for (int d = 1; d < L.ndims; d++) if (L.stride[k][d] == es(k)) { mine = d; break; }
+      if (mine < 0 || (tdim >= 0 && mine != tdim)) return false;
+      tdim = mine; staged |= (1u << k);
+   }
+   if (tdim < 0 || L.size[0] < 8 || L.size[tdim] < 8) return false;
+   uint64_t blocks = 1;
+   memset(&p, 0, sizeof(p));
+   for (int d = 0; d < L.ndims; d++) {
+      if (L.size[d] > 0x7FFFFFFFll) return false;
+      p.size[d] = (uint32_t)L.size[d];
+      p.div[d] = make_fastdiv(p.size[d]);
+      for (int k = 0; k < NOPS; k++) p.stride[k][d] = L.stride[k][d];
+      blocks *= (d == 0 || d == tdim) ? (uint64_t)((L.size[d] + EW_TILE - 1) / EW_TILE) : (uint64_t)L.size[d];
+   }
+   if (blocks > 0x7FFFFFFFull) return false;
+   for (int k = 0; k < NOPS; k++) p.ptr[k] = L.ptr[k];
+   p.ndims = L.ndims; p.tdim = tdim; p.staged = staged;
+   p.tiles0 = (uint32_t)((L.size[0] + EW_TILE - 1) / EW_TILE);
+   p.tilesT = (uint32_t)((L.size[tdim] + EW_TILE - 1) / EW_TILE);
+   p.div_tiles0 = make_fastdiv(p.tiles0); p.div_tilesT = make_fastdiv(p.tilesT);
+   return true;
+}
+
 // ---------------------------------------------------------------------------
 // Host side: pick the variant and launch.
 // ---------------------------------------------------------------------------
@@ -335,6 +475,20 @@ int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
       else                         ew_contig<A, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
       SD_LAUNCH_CHECK();
       return 0;
+   }
+
+   // a source dense along another dimension than the destination: shared-memory tiles
+   if constexpr (NIN >= 1) {
+      if (!dense0 && !unal) {
+         EwTiledParams<NOPS> tp;
+         if (ew_plan_tiled<A>(L, tp)) {
+            uint64_t blocks = (uint64_t)tp.tiles0 * tp.tilesT;
+            for (int d = 1; d < L.ndims; d++) if (d != tp.tdim) blocks *= (uint64_t)L.size[d];
+            ew_tiled<A><<<(unsigned)blocks, EW_THREADS, 0, stream>>>(apply, tp);
+            SD_LAUNCH_CHECK();
+            return 0;
+         }
+      }
    }
 
    // strided: can the innermost dimension be vectorised?

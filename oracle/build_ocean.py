@@ -6,7 +6,8 @@ TEST INFRASTRUCTURE.  Nothing here is part of the product: the outputs show that
 library is a drop-in for the reference's own callers, and let the reference's golden
 scripts (examples/python/gpu/{tensors,index}/*.py with their .ref files) run on it.
 
-Sources are compiled where they lie in the reference checkout ($OCEAN_REFERENCE_DIR); only
+Sources are compiled where they lie in the reference checkout ($OCEAN_REFERENCE_DIR, or a directory
+`reference` beside this repository); only
 outputs are written, all below oracle/_ref/ocean/ (git-ignored):
 
     lib/libocean_base.so   src/base/*.c
@@ -56,9 +57,10 @@ CFLAGS = ["-O2", "-std=gnu99", "-fPIC", "-fopenmp", "-fno-strict-aliasing", "-w"
 
 
 def reference_dir() -> Path | None:
-    d = os.environ.get("OCEAN_REFERENCE_DIR")
-    if d and (Path(d) / "src" / "core" / "gpu").is_dir():
-        return Path(d)
+    """The reference checkout: $OCEAN_REFERENCE_DIR, else a directory named `reference` beside this repository."""
+    for cand in (os.environ.get("OCEAN_REFERENCE_DIR"), ROOT.parent / "reference"):
+        if cand and (Path(cand) / "src" / "core" / "gpu").is_dir():
+            return Path(cand)
     return None
 
 
@@ -228,5 +230,5 @@ if __name__ == "__main__":
     ap.add_argument("-j", type=int, default=None)
     a = ap.parse_args()
     if reference_dir() is None:
-        sys.exit("set OCEAN_REFERENCE_DIR to the reference checkout")
+        sys.exit("no reference checkout: set OCEAN_REFERENCE_DIR")
     build(a.force, a.j)

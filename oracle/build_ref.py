@@ -36,8 +36,11 @@ LIB = OUT / "libsolid_core_cpu.so"
 
 
 def reference_root() -> Path | None:
-    root = Path(os.environ.get("OCEAN_REFERENCE_DIR", "/root/reference"))
-    return root if (root / "solid" / "src" / "core" / "cpu").is_dir() else None
+    """The reference checkout: $OCEAN_REFERENCE_DIR, else a directory named `reference` beside this repository."""
+    for cand in (os.environ.get("OCEAN_REFERENCE_DIR"), HERE.parent.parent / "reference"):
+        if cand and (Path(cand) / "solid" / "src" / "core" / "cpu").is_dir():
+            return Path(cand)
+    return None
 
 
 def _run(cmd, **kw):
