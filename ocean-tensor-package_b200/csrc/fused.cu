@@ -26,6 +26,7 @@ namespace sd {
 // axpy + sums
 // ===========================================================================
 constexpr int AX_THREADS = 256;
+constexpr int AX_FOLD = 4096;                // per-block pairs folded into one second-level pair
 
 template <class T> struct Sums { T s, s2; };
 
@@ -141,8 +142,6 @@ __global__ void __launch_bounds__(AX_THREADS) axpy_sums_kernel(uint64_t n, T a, 
 // chunk per block (measured on B200: 7.1 TB/s against 6.4 TB/s for a grid of resident blocks that
 // stride through the arrays), so a large tensor leaves up to a million partials; they are folded in two
 // levels, AX_FOLD to one and then the rest in a single block.
-constexpr int AX_FOLD = 4096;
-
 template <class T>
 __global__ void __launch_bounds__(AX_THREADS) axpy_sums_finish(uint64_t nparts, int fold,
                                                                const Sums<T> *__restrict__ partials,
