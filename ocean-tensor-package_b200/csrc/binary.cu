@@ -64,44 +64,44 @@ template <class T> struct AxpyApply {
    // overflow, inf, nan) sends the whole vector through the per-element form above, out of line.
    template <int N> SD_D Vec<T, N> vec(const Vec<T, N> &x, const Vec<T, N> &y) const
    {
-      if constexpr (is_half<T>) {
+      if constexpr (is_half<T> && (N % 2 == 0)) {
+         // Two halves per 32-bit word, converted by the PACKED instructions (cvt.f32.f16 issues on the
+         // special-function pipe, a few lanes per cycle: with one conversion per element this kernel ran at
+         // 4.2 TB/s bound by that pipe, with one per pair it runs at the HBM rate).
          const float af = __half2float(__ushort_as_half(a.v));
+         uint32_t xw[N / 2], yw[N / 2];
+         memcpy(xw, &x, sizeof(xw)); memcpy(yw, &y, sizeof(yw));
          float w[N];
          // magnitude bits of every product and of every sum: smallest and largest over the vector
          uint32_t plo = 0x7FFFFFFFu, phi = 0u, slo = 0x7FFFFFFFu, shi = 0u;
 #pragma unroll
-         for (int j = 0; j < N; j += 2) {
-            float s[2]; uint32_t pm[2], sm[2];
+         for (int k = 0; k < N / 2; k++) {
+            const float2 xf = __half22float2(*reinterpret_cast<const __half2 *>(&xw[k]));
+            const float2 yf = __half22float2(*reinterpret_cast<const __half2 *>(&yw[k]));
+            const float xs[2] = { xf.x, xf.y }, ys[2] = { yf.x, yf.y };
+            uint32_t pm[2], sm[2];
 #pragma unroll
-            for (int e = 0; e < 2 && j + e < N; e++) {
-               const float xf = __half2float(__ushort_as_half(x.v[j + e].v)), yf = __half2float(__ushort_as_half(y.v[j + e].v));
-               const uint32_t praw = __float_as_uint(af * xf);
+            for (int e = 0; e < 2; e++) {
+               const uint32_t praw = __float_as_uint(af * xs[e]);
                pm[e] = praw & 0x7FFFFFFFu;
-               s[e] = __uint_as_float((praw + 0x1000u) & 0xFFFFE000u) + yf;
-               const uint32_t sraw = __float_as_uint(s[e]);
+               const uint32_t sraw = __float_as_uint(__uint_as_float((praw + 0x1000u) & 0xFFFFE000u) + ys[e]);
                sm[e] = sraw & 0x7FFFFFFFu;
-               w[j + e] = __uint_as_float((sraw + 0x1000u) & 0xFFFFE000u);
+               w[2 * k + e] = __uint_as_float((sraw + 0x1000u) & 0xFFFFE000u);
             }
-            if (j + 1 < N) {
-               plo = __vimin3_u32(plo, pm[0], pm[1]); phi = __vimax3_u32(phi, pm[0], pm[1]);
-               slo = __vimin3_u32(slo, sm[0], sm[1]); shi = __vimax3_u32(shi, sm[0], sm[1]);
-            } else {
-               plo = min(plo, pm[0]); phi = max(phi, pm[0]); slo = min(slo, sm[0]); shi = max(shi, sm[0]);
-            }
+            plo = __vimin3_u32(plo, pm[0], pm[1]); phi = __vimax3_u32(phi, pm[0], pm[1]);
+            slo = __vimin3_u32(slo, sm[0], sm[1]); shi = __vimax3_u32(shi, sm[0], sm[1]);
          }
          // 2^-14 <= |product| < 2^15 and 2^-14 <= |sum| < 2^16 (nan and inf have the largest magnitude bits)
          const bool plain = plo >= 0x38800000u && phi < 0x47000000u && slo >= 0x38800000u && shi < 0x47800000u;
-         Vec<T, N> o;
-         if (plain) {
+         if (!plain) return rare<N>(x, y);
+         uint32_t ow[N / 2];
 #pragma unroll
-            for (int j = 0; j + 1 < N; j += 2) {
-               const __half2 h = __floats2half2_rn(w[j], w[j + 1]);
-               o.v[j].v = __half_as_ushort(__low2half(h)); o.v[j + 1].v = __half_as_ushort(__high2half(h));
-            }
-            if (N & 1) o.v[N - 1].v = __half_as_ushort(__float2half_rn(w[N - 1]));
-         } else {
-            o = rare<N>(x, y);
+         for (int k = 0; k < N / 2; k++) {
+            const __half2 h = __floats2half2_rn(w[2 * k], w[2 * k + 1]);
+            memcpy(&ow[k], &h, 4);
          }
+         Vec<T, N> o;
+         memcpy(&o, ow, sizeof(ow));
          return o;
       } else {
          Vec<T, N> o;
