@@ -44,6 +44,28 @@ SD_DEFINE_SCALAR(bitwise_xor_scalar, bitwise_xor, integer_bool)
 // multiplyScalar followed by add produces (src/core/interface/tensor_itf.c:4221-4251),
 // in one pass.  Real floating-point types.
 namespace sd {
+// z = half(half(a * x) + y) element by element with the general conversions, for eight halves in four words
+__device__ __noinline__ inline uint4 axpy_half_rare8(uint32_t abits, uint4 x, uint4 y)
+{
+   Half a; a.v = (uint16_t)abits;
+   const uint32_t xs[4] = { x.x, x.y, x.z, x.w }, ys[4] = { y.x, y.y, y.z, y.w };
+   uint32_t o[4];
+   const float af = half_to_float(a);
+#pragma unroll
+   for (int k = 0; k < 4; k++) {
+      uint32_t r = 0;
+#pragma unroll
+      for (int e = 0; e < 2; e++) {
+         Half xh, yh; xh.v = (uint16_t)(xs[k] >> (16 * e)); yh.v = (uint16_t)(ys[k] >> (16 * e));
+         const Half prod = float_to_half(af * half_to_float(xh));
+         const Half z = float_to_half(half_to_float(prod) + half_to_float(yh));
+         r |= (uint32_t)z.v << (16 * e);
+      }
+      o[k] = r;
+   }
+   return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
 template <class T> struct AxpyApply {
    static constexpr int NIN = 2;
    static constexpr bool VECTOR = is_half<T>;
@@ -61,7 +83,7 @@ template <class T> struct AxpyApply {
    // "add half a unit of the 13 dropped bits, clear them".  The inputs then need the hardware conversion only
    // (its one difference from half.c, -0 for +0, cannot survive a non-zero product or sum), and the result is
    // exactly representable, so the hardware conversion back is exact.  One out-of-range element (zero, subnormal,
-   // overflow, inf, nan) sends the whole vector through the per-element form above, out of line.
+   // overflow, inf, nan) sends the whole vector through the per-element form, out of line.
    template <int N> SD_D Vec<T, N> vec(const Vec<T, N> &x, const Vec<T, N> &y) const
    {
       if constexpr (is_half<T> && (N % 2 == 0)) {
@@ -93,7 +115,21 @@ template <class T> struct AxpyApply {
          }
          // 2^-14 <= |product| < 2^15 and 2^-14 <= |sum| < 2^16 (nan and inf have the largest magnitude bits)
          const bool plain = plo >= 0x38800000u && phi < 0x47000000u && slo >= 0x38800000u && shi < 0x47800000u;
-         if (!plain) return rare<N>(x, y);
+         if (!plain) {
+            if constexpr (N == 8) {
+               // out of line, operands BY VALUE in registers: a call that takes them by reference (or as a member
+               // function of this object) makes the compiler keep a copy of x, y and the object in local memory
+               // for every vector, rare or not -- measured as 1.5 million local stores per launch and a third of
+               // the run time
+               const uint4 r = axpy_half_rare8(a.v, make_uint4(xw[0], xw[1], xw[2], xw[3]), make_uint4(yw[0], yw[1], yw[2], yw[3]));
+               Vec<T, N> o; memcpy(&o, &r, 16); return o;
+            } else {
+               Vec<T, N> o;
+#pragma unroll
+               for (int j = 0; j < N; j++) o.v[j] = (*this)(x.v[j], y.v[j]);
+               return o;
+            }
+         }
          uint32_t ow[N / 2];
 #pragma unroll
          for (int k = 0; k < N / 2; k++) {
@@ -110,14 +146,53 @@ template <class T> struct AxpyApply {
          return o;
       }
    }
-   template <int N> __device__ __noinline__ Vec<T, N> rare(Vec<T, N> x, Vec<T, N> y) const      // by value: stays in registers
-   {
-      Vec<T, N> o;
-#pragma unroll
-      for (int j = 0; j < N; j++) o.v[j] = (*this)(x.v[j], y.v[j]);
-      return o;
-   }
 };
+// Dense half tensors: eight halves per 16-byte access, four accesses per operand in flight, one chunk per block,
+// and nothing else in the kernel (no broadcast, alignment or stride cases): the general engine runs the same
+// arithmetic at 4.2-4.7 TB/s, this form at the HBM rate (6.2 TB/s on 2^26 elements).
+constexpr int AXH_U = 4;
+__global__ void __launch_bounds__(EW_THREADS) axpy_half_dense(const AxpyApply<Half> apply, const uint4 *__restrict__ x,
+                                                              const uint4 *__restrict__ y, uint4 *__restrict__ z, uint64_t nvec)
+{
+   const uint64_t base = (uint64_t)blockIdx.x * (EW_THREADS * AXH_U) + threadIdx.x;
+   uint4 vx[AXH_U], vy[AXH_U];
+#pragma unroll
+   for (int u = 0; u < AXH_U; u++) {
+      const uint64_t i = base + (uint64_t)u * EW_THREADS;
+      if (i < nvec) { vx[u] = __ldcs(x + i); vy[u] = __ldcs(y + i); }
+   }
+#pragma unroll
+   for (int u = 0; u < AXH_U; u++) {
+      const uint64_t i = base + (uint64_t)u * EW_THREADS;
+      if (i < nvec) {
+         Vec<Half, 8> a, b; memcpy(&a, &vx[u], 16); memcpy(&b, &vy[u], 16);
+         const Vec<Half, 8> o = apply.template vec<8>(a, b);
+         uint4 r; memcpy(&r, &o, 16);
+         __stcs(z + i, r);
+      }
+   }
+}
+// Runs the dedicated kernel on the whole vectors of one dense, 16-byte aligned run of halves and shortens the
+// layout to what is left (possibly nothing); other types and layouts are left untouched for the engine.
+template <class T> int axpy_dense_part(const AxpyApply<T> &ap, Layout<3> &L, cudaStream_t stream)
+{
+   if constexpr (is_half<T>) {
+      if (L.ndims == 1 && L.nelem >= 8 && L.stride[0][0] == 2 && L.stride[1][0] == 2 && L.stride[2][0] == 2 &&
+          aligned_to(L.ptr[0], 16) && aligned_to(L.ptr[1], 16) && aligned_to(L.ptr[2], 16)) {
+         const uint64_t nvec = (uint64_t)L.nelem / 8;
+         const uint64_t blocks = (nvec + EW_THREADS * AXH_U - 1) / (EW_THREADS * AXH_U);
+         if (blocks <= 0x7FFFFFFFull) {
+            axpy_half_dense<<<(unsigned)blocks, EW_THREADS, 0, stream>>>(
+               ap, (const uint4 *)L.ptr[0], (const uint4 *)L.ptr[1], (uint4 *)L.ptr[2], nvec);
+            SD_LAUNCH_CHECK();
+            const int64_t done = (int64_t)(nvec * 8);
+            for (int k = 0; k < 3; k++) L.ptr[k] += done * 2;
+            L.size[0] -= done; L.nelem -= done;
+         }
+      }
+   }
+   return 0;
+}
 } // namespace sd
 SD_WHEN(real)(
 extern "C" int SD_PASTE(solid_gpu_axpy_, SDX)(SOLID_GPU_ARGS_AXPY)
@@ -126,5 +201,7 @@ extern "C" int SD_PASTE(solid_gpu_axpy_, SDX)(SOLID_GPU_ARGS_AXPY)
    sd::Layout<3> L;
    if (sd::make_layout<3>(L, ndims, size, st, pt, 2) != 0) return -1;
    sd::AxpyApply<T> ap; memcpy(&ap.a, &a, sizeof(T));
+   if (sd::axpy_dense_part<T>(ap, L, stream) != 0) return -1;
+   if (L.nelem == 0) return 0;
    return sd::ew_launch(ap, L, stream);
 })

@@ -328,16 +328,30 @@ __global__ void __launch_bounds__(EW_THREADS) ew_tiled(const A apply, const EwTi
    }
    const uint32_t size0 = p.size[0], sizeT = p.size[T];
 
+   // Sources that are NOT staged are loaded first, in the mapping of the second phase (thread (tx, ty): position tx
+   // along 0, ty + ROWS j along T), so that they are in flight together with the staged loads below instead of
+   // after the barrier.
+   const uint32_t i0 = base0 + tx;
+   in1_t a[PER]; in2_t b[PER];
+#pragma unroll
+   for (int j = 0; j < PER; j++) {
+      const uint32_t iT = baseT + ty + ROWS * j;
+      if (i0 < size0 && iT < sizeT) {
+         if constexpr (NIN >= 1) if (!(p.staged & 1u)) a[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)i0 * p.stride[0][0] + (int64_t)iT * p.stride[0][T]);
+         if constexpr (NIN >= 2) if (!(p.staged & 2u)) b[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)i0 * p.stride[1][0] + (int64_t)iT * p.stride[1][T]);
+      }
+   }
+
    // park the sources that are dense along T: thread (tx, ty) reads positions (ty + ROWS j) along 0, tx along T
-   if (p.staged) {
+   {
       in1_t r1[PER]; in2_t r2[PER];
-      const uint32_t iT = baseT + tx;
+      const uint32_t jT = baseT + tx;
 #pragma unroll
       for (int j = 0; j < PER; j++) {
-         const uint32_t i0 = base0 + ty + ROWS * j;
-         if (i0 < size0 && iT < sizeT) {
-            if constexpr (NIN >= 1) if (p.staged & 1u) r1[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)i0 * p.stride[0][0] + (int64_t)iT * p.stride[0][T]);
-            if constexpr (NIN >= 2) if (p.staged & 2u) r2[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)i0 * p.stride[1][0] + (int64_t)iT * p.stride[1][T]);
+         const uint32_t j0 = base0 + ty + ROWS * j;
+         if (j0 < size0 && jT < sizeT) {
+            if constexpr (NIN >= 1) if (p.staged & 1u) r1[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)j0 * p.stride[0][0] + (int64_t)jT * p.stride[0][T]);
+            if constexpr (NIN >= 2) if (p.staged & 2u) r2[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)j0 * p.stride[1][0] + (int64_t)jT * p.stride[1][T]);
          }
       }
 #pragma unroll
@@ -348,22 +362,11 @@ __global__ void __launch_bounds__(EW_THREADS) ew_tiled(const A apply, const EwTi
       __syncthreads();
    }
 
-   // walk the tile along dimension 0: thread (tx, ty) handles positions tx along 0, (ty + ROWS j) along T
-   const uint32_t i0 = base0 + tx;
-   in1_t a[PER]; in2_t b[PER];
+   // walk the tile along dimension 0
 #pragma unroll
    for (int j = 0; j < PER; j++) {
-      const uint32_t iT = baseT + ty + ROWS * j;
-      if (i0 < size0 && iT < sizeT) {
-         if constexpr (NIN >= 1) {
-            if (p.staged & 1u) a[j] = tile1[tx][ty + ROWS * j];
-            else a[j] = ld_one<in1_t>(p.ptr[0] + off[0] + (int64_t)i0 * p.stride[0][0] + (int64_t)iT * p.stride[0][T]);
-         }
-         if constexpr (NIN >= 2) {
-            if (p.staged & 2u) b[j] = tile2[tx][ty + ROWS * j];
-            else b[j] = ld_one<in2_t>(p.ptr[1] + off[1] + (int64_t)i0 * p.stride[1][0] + (int64_t)iT * p.stride[1][T]);
-         }
-      }
+      if constexpr (NIN >= 1) if (p.staged & 1u) a[j] = tile1[tx][ty + ROWS * j];
+      if constexpr (NIN >= 2) if (p.staged & 2u) b[j] = tile2[tx][ty + ROWS * j];
    }
 #pragma unroll
    for (int j = 0; j < PER; j++) {

@@ -399,19 +399,19 @@ template <class C> SD_D void store_as(char *p, int dtype, C v, bool swap, bool u
 
 // Linear variant for one merged dimension: a block handles 256 x MR consecutive elements, a
 // thread MR of them 256 apart (coalesced), all loads issued before the first conversion.
-// Tile of the tiled variant: 32 x 32 elements, four per thread and operand, built for six resident blocks of 256
-// threads (40 registers, nothing spilled).  An earlier 32 x 64 tile with eight elements per thread needed 48
-// registers for five blocks and spilled (the capture showed a million local-memory requests per launch).
+// Tile of the tiled variant.  Measured on B200 (4096^2, f64 transposed x i32 byte-swapped + f32 row -> f32): the
+// shape (16x128, 32x64, 64x32) makes no difference, resident warps do: 3, 4, 5, 6 blocks of 256 threads per
+// multiprocessor ran at 78, 68, 62, 65 us, so the kernel is built for five (48 registers, a few spills).
 #ifndef MIX_M0
 #define MIX_M0 32
-#define MIX_M1 32
+#define MIX_M1 64
 #define MIX_NT 256
-#define MIX_BLOCKS 6
+#define MIX_BLOCKS 5
 #endif
 constexpr int M0 = MIX_M0;                  // tile extent along dimension 0
 constexpr int M1 = MIX_M1;                  // tile extent along dimension dt
 constexpr int MT = MIX_NT;                  // threads of a tile
-constexpr int MR = M0 * M1 / MT;             // elements per thread and operand
+constexpr int MR = 8;                       // elements per thread and operand
 static_assert(M0 * M1 == MT * MR, "tile and thread count do not match");
 constexpr int MP1 = MT / M1;                // rows of dimension 0 per pass of phase 1
 constexpr int MP2 = MT / M0;                // rows of dimension dt per pass of phase 2
@@ -443,10 +443,10 @@ __global__ void __launch_bounds__(256) mix_linear(const MixParams p)
    }
 }
 
-// Tiled variant for two or more dimensions: a tile of M0 (dimension 0) x M1 (dimension dt)
-// elements, 256 threads, MR elements per thread and operand.  Operands that are dense along dt
-// (a transposed matrix) are first read with M1 lanes running along dt, converted and parked in
-// shared memory; then M0 lanes run along dimension 0, the remaining operands are read
+// Tiled variant for two or more dimensions: a tile of 32 (dimension 0) x 64 (dimension dt)
+// elements, 256 threads, 8 elements per thread and operand.  Operands that are dense along dt
+// (a transposed matrix) are first read with 64 lanes running along dt, converted and parked in
+// shared memory; then 32 lanes run along dimension 0, the remaining operands are read
 // directly (coalesced) and the result is stored.  In both phases a thread issues all loads of
 // an operand before it consumes any of them.
 template <class C, bool FULL>

@@ -12,9 +12,9 @@ GPU tier (needs only what oracle/build_ocean.py left under oracle/_ref/ocean, wh
   * the reference's GPU golden scripts, examples/python/gpu/{tensors,index}/NAME.py, print exactly NAME.ref
     - with the reference's UNCHANGED GPU module (its own dispatch files) over this Solid library, and
     - with this repository's dispatch registered in OcModuleCore (csrc/ocean_module.c + libocean_gpu_b200.so);
-  * the reference's CPU golden scripts examples/python/cpu/tensors/NAME.py, re-targeted to ocean.gpu[0], print
-    NAME.ref with the device name replaced: the whole interface layer (promotion, broadcasting, byte order,
-    temporaries, in-place forms) then runs on these kernels.
+  * the reference's CPU golden scripts examples/python/cpu/tensors/NAME.py, re-targeted to ocean.gpu[0] on this
+    repository's dispatch, print NAME.ref with the device name replaced: the whole interface layer (promotion,
+    broadcasting, byte order, temporaries, in-place forms) then runs on these kernels.
 """
 from __future__ import annotations
 
@@ -211,12 +211,22 @@ TWO_GPUS = {"tensor_copy_09", "tensor_device_cast_01"}
 # which is the oracle here, replaces only the NaNs; the CPU golden of the same script says what that prints.
 CPU_REF_INSTEAD = {"tensor_fillnan_01"}
 
+# Lines that are a bare Python float, which Python 2 (the .ref files' interpreter) printed with 12 significant digits
+# and Python 3 prints in full: compared as numbers.
+PY2_FLOAT_LINES = {"tensor_axis_norm2_01": [-1]}
+
 # cpu/tensors scripts whose .ref cannot be reproduced on ocean.gpu[0] for reasons outside these kernels
 RETARGET_EXCLUDED = {
     # Python-2 era artefacts in the .ref files themselves (they fail on the reference's own CPU device too)
     "ocean_astensor_03": "py2 repr in .ref", "ocean_astensor_06": "py2 repr in .ref", "ocean_cast_05": "py2 repr in .ref",
     "ocean_divide_01": "py2 integer division in the script", "ocean_norm_01": "py2 artefact in .ref",
 }
+
+
+def _no_device_names(text: str) -> str:
+    text = re.sub(r" on (cpu|gpu\d+)", " on DEVICE", text)
+    text = re.sub(r"device '(cpu|gpu\d+)'", "device 'DEVICE'", text)
+    return re.sub(r"(is not available for type \w+ on) (CPU|GPU)", r"\1 DEVICE", text)
 
 
 def _retargeted(script: Path, tmp: Path) -> Path:
@@ -244,13 +254,13 @@ def golden_outputs():
                 continue
             src = OCEAN / "examples" / rel
             jobs.append(((variant, str(rel)), src, src.parent, _env(variant)))
-        for rel in CPU_SCRIPTS:
-            if rel.stem in RETARGET_EXCLUDED:
-                continue
-            d = tmp / variant
-            d.mkdir(exist_ok=True)
-            jobs.append(((variant, str(rel)), _retargeted(OCEAN / "examples" / rel, d), d, _env(variant)))
-    with ThreadPoolExecutor(8) as pool:
+    for rel in CPU_SCRIPTS:                                   # re-targeted CPU goldens: on this repository's dispatch
+        if rel.stem in RETARGET_EXCLUDED:
+            continue
+        d = tmp / "b200"
+        d.mkdir(exist_ok=True)
+        jobs.append((("b200", str(rel)), _retargeted(OCEAN / "examples" / rel, d), d, _env("b200")))
+    with ThreadPoolExecutor(min(16, (os.cpu_count() or 8))) as pool:
         outs = list(pool.map(lambda j: _run_script(j[1], j[2], j[3]), jobs))
     return {j[0]: o for j, o in zip(jobs, outs)}
 
@@ -266,7 +276,15 @@ def test_reference_gpu_golden(rel, variant, golden_outputs):
     want = ref.read_text()
     if rel.stem in CPU_REF_INSTEAD:
         want = (OCEAN / "examples" / "cpu" / "tensors" / (rel.stem + ".ref")).read_text().replace(" on cpu>", " on gpu0>")
-    assert golden_outputs[key] == want
+    got = golden_outputs[key]
+    if rel.stem in PY2_FLOAT_LINES:                           # a Python float printed with 12 digits by Python 2
+        gl, wl = got.splitlines(), want.splitlines()
+        assert len(gl) == len(wl)
+        for k in PY2_FLOAT_LINES[rel.stem]:
+            assert abs(float(gl[k]) - float(wl[k])) <= 1e-11 * abs(float(wl[k])), (gl[k], wl[k])
+            gl[k] = wl[k]
+        got, want = "\n".join(gl), "\n".join(wl)
+    assert got == want
 
 
 # Differences between a CPU golden and its run on ocean.gpu[0] that do not come from these kernels; each entry says
@@ -275,12 +293,13 @@ RETARGET_KNOWN = {}
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("variant", ["reference", "b200"])
 @pytest.mark.parametrize("rel", CPU_SCRIPTS, ids=[str(r) for r in CPU_SCRIPTS])
-def test_reference_cpu_golden_on_gpu(rel, variant, golden_outputs):
+def test_reference_cpu_golden_on_gpu(rel, golden_outputs):
     if rel.stem in RETARGET_EXCLUDED:
         pytest.skip(RETARGET_EXCLUDED[rel.stem])
-    if (rel.stem, variant) in RETARGET_KNOWN or (rel.stem, "both") in RETARGET_KNOWN:
-        pytest.skip(RETARGET_KNOWN.get((rel.stem, variant)) or RETARGET_KNOWN[(rel.stem, "both")])
-    want = (OCEAN / "examples" / rel.with_suffix(".ref")).read_text().replace(" on cpu>", " on gpu0>")
-    assert golden_outputs[(variant, str(rel))] == want
+    if rel.stem in RETARGET_KNOWN:
+        pytest.skip(RETARGET_KNOWN[rel.stem])
+    # Only the DEFAULT device is re-targeted: tensors that a script places on ocean.cpu by name, or that the
+    # interface creates there, stay there, so device names are taken out of the comparison on both sides.
+    want = _no_device_names((OCEAN / "examples" / rel.with_suffix(".ref")).read_text())
+    assert _no_device_names(golden_outputs[("b200", str(rel))]) == want
