@@ -151,18 +151,19 @@ template <class T> struct AxpyApply {
 // and nothing else in the kernel (no broadcast, alignment or stride cases): the general engine runs the same
 // arithmetic at 4.2-4.7 TB/s, this form at the HBM rate (6.2 TB/s on 2^26 elements).
 constexpr int AXH_U = 4;
+template <int AXH_UNROLL>          // a template so that the per-type units of this file share one definition
 __global__ void __launch_bounds__(EW_THREADS) axpy_half_dense(const AxpyApply<Half> apply, const uint4 *__restrict__ x,
                                                               const uint4 *__restrict__ y, uint4 *__restrict__ z, uint64_t nvec)
 {
-   const uint64_t base = (uint64_t)blockIdx.x * (EW_THREADS * AXH_U) + threadIdx.x;
-   uint4 vx[AXH_U], vy[AXH_U];
+   const uint64_t base = (uint64_t)blockIdx.x * (EW_THREADS * AXH_UNROLL) + threadIdx.x;
+   uint4 vx[AXH_UNROLL], vy[AXH_UNROLL];
 #pragma unroll
-   for (int u = 0; u < AXH_U; u++) {
+   for (int u = 0; u < AXH_UNROLL; u++) {
       const uint64_t i = base + (uint64_t)u * EW_THREADS;
       if (i < nvec) { vx[u] = __ldcs(x + i); vy[u] = __ldcs(y + i); }
    }
 #pragma unroll
-   for (int u = 0; u < AXH_U; u++) {
+   for (int u = 0; u < AXH_UNROLL; u++) {
       const uint64_t i = base + (uint64_t)u * EW_THREADS;
       if (i < nvec) {
          Vec<Half, 8> a, b; memcpy(&a, &vx[u], 16); memcpy(&b, &vy[u], 16);
@@ -182,7 +183,7 @@ template <class T> int axpy_dense_part(const AxpyApply<T> &ap, Layout<3> &L, cud
          const uint64_t nvec = (uint64_t)L.nelem / 8;
          const uint64_t blocks = (nvec + EW_THREADS * AXH_U - 1) / (EW_THREADS * AXH_U);
          if (blocks <= 0x7FFFFFFFull) {
-            axpy_half_dense<<<(unsigned)blocks, EW_THREADS, 0, stream>>>(
+            axpy_half_dense<AXH_U><<<(unsigned)blocks, EW_THREADS, 0, stream>>>(
                ap, (const uint4 *)L.ptr[0], (const uint4 *)L.ptr[1], (uint4 *)L.ptr[2], nvec);
             SD_LAUNCH_CHECK();
             const int64_t done = (int64_t)(nvec * 8);
