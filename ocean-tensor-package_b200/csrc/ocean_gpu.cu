@@ -36,7 +36,7 @@ template <class F> F lookup(F const *table, int dtype, const char *desc)
 {
    if (!valid_dtype(dtype)) { fail("Invalid data type index %d", dtype); return nullptr; }
    F f = table[dtype];
-   if (f == nullptr) fail("Function %s is not supported for type %s on GPU", desc, dtype_names[dtype]);
+   if (f == nullptr) fail("The %s function is not available for type %s on GPU", desc, dtype_names[dtype]);
    return f;
 }
 
@@ -558,9 +558,11 @@ extern "C" int OcTensorGPU_byteswapNoFlag(const OcTensorView *t)
    return update(t);
 }
 
+// The scalar arrives as the bytes to store: for a byte-swapped tensor the interface layer has already reversed them
+// (OcTensor_fill, src/core/interface/tensor_itf.c:2770-2784), so the destination's byte order does not matter here.
 static int fill_common(const OcTensorView *t, const OcScalarView *s, solid_funptr_gpu_fill const *table, const char *desc)
 {
-   if (check_elemwise(t, "destination") != 0) return -1;
+   if (check_view(t, "destination") != 0) return -1;
    if (s == nullptr || s->dtype != t->dtype) return fail("The scalar must have the data type of the tensor");
    solid_funptr_gpu_fill f = lookup(table, t->dtype, desc);
    if (f == nullptr || set_device(t->device) != 0) return -1;
@@ -572,7 +574,7 @@ extern "C" int OcTensorGPU_fillNaN(const OcTensorView *t, const OcScalarView *s)
 
 extern "C" int OcTensorGPU_maskedFill(const OcTensorView *t, const OcTensorView *mask, const OcScalarView *s)
 {
-   if (check_elemwise(t, "destination") != 0 || check_elemwise(mask, "mask") != 0) return -1;
+   if (check_view(t, "destination") != 0 || check_elemwise(mask, "mask") != 0) return -1;
    if (mask->dtype != SD_BOOL) return fail("The mask must have type bool");
    if (!same_shape(t, mask)) return fail("Tensor size mismatch in maskedFill");
    if (s == nullptr || s->dtype != t->dtype) return fail("The scalar must have the data type of the tensor");

@@ -38,6 +38,7 @@
 #include "ocean/core/gpu/cuda.h"
 #include "ocean/base/shape.h"
 #include "ocean/base/error.h"
+#include "ocean/external/ocean-solid/ocean_solid.h"
 
 #include "ocean_gpu_b200.h"
 
@@ -82,9 +83,14 @@ static int report(int status)
 /* Unary and binary elementwise operations                                                    */
 /* ------------------------------------------------------------------------------------------ */
 
+/* The table look-up is repeated here with the reference's own macro so that a missing type raises the reference's  */
+/* message, description included ("The unary negative function is not available for type uint8 on GPU").            */
 #define OC_TEMPLATE(NAME, SOLID_OP, CHECK, DESC) \
 static int b200_##NAME(OcTensor *src, OcTensor *dst) \
 {  OcTensorView vs, vd; \
+   solid_funptr_gpu_##SOLID_OP funptr; \
+   OC_SOLID_FUNPTR(DESC, solid_gpu_##SOLID_OP, funptr, src -> dtype, "GPU"); \
+   if (funptr == 0) return -1; \
    view_of(src, &vs); view_of(dst, &vd); \
    return report(OcTensorGPU_##NAME(&vs, &vd)); \
 }
@@ -101,6 +107,9 @@ void OcTensorGPU_initializeUnaryOps(OcModuleCore *module)
 #define OC_TEMPLATE(NAME, SOLID_OP, CHECK, DESC) \
 static int b200_##NAME(OcTensor *src1, OcTensor *src2, OcTensor *dst) \
 {  OcTensorView v1, v2, vd; \
+   solid_funptr_gpu_##SOLID_OP funptr; \
+   OC_SOLID_FUNPTR(DESC, solid_gpu_##SOLID_OP, funptr, src1 -> dtype, "GPU"); \
+   if (funptr == 0) return -1; \
    view_of(src1, &v1); view_of(src2, &v2); view_of(dst, &vd); \
    return report(OcTensorGPU_##NAME(&v1, &v2, &vd)); \
 }

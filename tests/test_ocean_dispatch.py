@@ -67,12 +67,12 @@ def test_reduction_result_types_agree_with_python_table():
 def test_errors_before_any_cuda_call():
     oc = _ocean.get()
     a, b, d = fake_view("float"), fake_view("float"), fake_view("float")
-    with pytest.raises(OceanError, match="not supported for type bool"):
+    with pytest.raises(OceanError, match="not available for type bool"):
         vb = fake_view("bool")
         oc._check(oc.fn("sin")(C.byref(vb), C.byref(vb)), "sin")
-    with pytest.raises(OceanError, match="not supported for type float"):
+    with pytest.raises(OceanError, match="not available for type float"):
         oc._check(oc.fn("bitwiseAnd")(C.byref(a), C.byref(b), C.byref(d)), "bitwiseAnd")
-    with pytest.raises(OceanError, match="not supported for type complex-double"):
+    with pytest.raises(OceanError, match="not available for type complex-double"):
         vc = fake_view("cdouble")
         oc._check(oc.fn("floorDivide")(C.byref(vc), C.byref(vc), C.byref(vc)), "floorDivide")
     with pytest.raises(OceanError, match="size mismatch"):

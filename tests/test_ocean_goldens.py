@@ -204,6 +204,10 @@ GPU_SCRIPTS = sorted(p.relative_to(OCEAN / "examples") for p in (OCEAN / "exampl
 CPU_SCRIPTS = sorted(p.relative_to(OCEAN / "examples") for p in (OCEAN / "examples" / "cpu" / "tensors").glob("*.py")) \
     if (OCEAN / "examples" / "cpu").exists() else []
 
+# gpu/tensors scripts that expect "Device gpu0 requires data to be aligned": this repository's module clears that
+# requirement (its copy kernels take any address), so on the b200 variant the tensor is simply created.
+ALIGNMENT_ERROR_EXPECTED = {"tensor_create_01", "tensor_create_02"}
+
 # Scripts that place tensors on a second GPU
 TWO_GPUS = {"tensor_copy_09", "tensor_device_cast_01"}
 # gpu/tensors/tensor_fillnan_01.ref was recorded from the reference's GPU kernels, whose fill_nan launches the plain
@@ -217,6 +221,19 @@ PY2_FLOAT_LINES = {"tensor_axis_norm2_01": [-1]}
 
 # cpu/tensors scripts whose .ref cannot be reproduced on ocean.gpu[0] for reasons outside these kernels
 RETARGET_EXCLUDED = {
+    "ctypes_01": "fills the tensor through a host pointer to its data (ctypes): not possible for device memory",
+    # GEMM on the GPU is the reference's own cuBLAS dispatch (src/core/gpu/op/tensor_blas_gpu.c, unchanged and outside
+    # the path this repository replaces); three of its scripts do not reproduce the CPU goldens there
+    "ocean_gemm_05": "reference GEMM path on cuBLAS (crashes inside the unchanged reference file)",
+    "ocean_gemm_09c": "reference GEMM path on cuBLAS", "ocean_gemm_09d": "reference GEMM path on cuBLAS",
+    # Same-dtype copies between tensors of different shape: the reference's GPU (and CPU) Tensor_copy moves the bytes
+    # as one block whenever OcTensors_haveCompatibleLayout says so (src/base/tensor.c:756-787 merges dimensions from the
+    # LAST one, i.e. in C order), which pairs elements in memory order; the converting copy pairs them in column-major
+    # order.  The CPU goldens reach the converting form (int64 range -> float), the GPU reaches the block copy because
+    # the conversion has already happened on the host.  The reference's own GPU module prints the same as this one.
+    "tensor_reshape_01": "reference block-copy pairing (see comment)", "tensor_slice_01": "reference block-copy pairing",
+    "tensor_split_01": "reference block-copy pairing", "tensor_split_02": "reference block-copy pairing",
+    "tensor_split_03": "reference block-copy pairing",
     # Python-2 era artefacts in the .ref files themselves (they fail on the reference's own CPU device too)
     "ocean_astensor_03": "py2 repr in .ref", "ocean_astensor_06": "py2 repr in .ref", "ocean_cast_05": "py2 repr in .ref",
     "ocean_divide_01": "py2 integer division in the script", "ocean_norm_01": "py2 artefact in .ref",
@@ -277,6 +294,9 @@ def test_reference_gpu_golden(rel, variant, golden_outputs):
     if rel.stem in CPU_REF_INSTEAD:
         want = (OCEAN / "examples" / "cpu" / "tensors" / (rel.stem + ".ref")).read_text().replace(" on cpu>", " on gpu0>")
     got = golden_outputs[key]
+    if variant == "b200" and rel.stem in ALIGNMENT_ERROR_EXPECTED:
+        assert "requires data to be aligned" in want and "requires data to be aligned" not in got and "Traceback" not in got
+        return
     if rel.stem in PY2_FLOAT_LINES:                           # a Python float printed with 12 digits by Python 2
         gl, wl = got.splitlines(), want.splitlines()
         assert len(gl) == len(wl)
