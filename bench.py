@@ -779,6 +779,55 @@ def run_ours(args):
         dist.destroy_process_group()
 
 
+def run_peer_copy(args):
+    """`--peer-copy`: the cross-device copy of the dispatch library (one process, GPUs 0 and 1) against the plain
+    peer copy of the same bytes.  Cases: a dense float64 matrix (what cudaMemcpyPeerAsync can move too), and a
+    converting, transposing copy (int32 4096^2 viewed transposed on GPU 1 -> float64 dense on GPU 0) that the
+    reference stages through dense temporaries on both sides.  Time is measured with events on the destination's
+    stream; the source is read with plain loads over NVLink by a kernel running on the destination GPU."""
+    import torch
+    from solid_b200 import Tensor, ops
+    if torch.cuda.device_count() < 2:
+        print(json.dumps({"peer_copy": None, "unavailable": "needs two GPUs"}))
+        return
+    m = 4096
+    rng = np.random.default_rng(7)
+    rows = []
+
+    def timed(fn, iters=20):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+        with torch.cuda.device(0):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            for _ in range(iters):
+                fn()
+            b.record()
+            torch.cuda.synchronize(0); torch.cuda.synchronize(1)
+            return a.elapsed_time(b) / iters * 1e-3
+
+    D = rng.uniform(-1, 1, (m, m))
+    src64 = Tensor.from_numpy(np.asfortranarray(D), device="cuda:1")
+    dst64 = Tensor.empty([m, m], "double", device="cuda:0")
+    raw_src = src64.storage; raw_dst = dst64.storage
+    t_plain = timed(lambda: raw_dst[: 8 * m * m].copy_(raw_src[: 8 * m * m], non_blocking=True))
+    rows.append({"op": "cudaMemcpyPeerAsync f64 4096^2 (128 MiB), GPU 1 -> GPU 0", "us": t_plain * 1e6, "gbs": 8 * m * m / t_plain / 1e9})
+    t = timed(lambda: ops.copy(src64, dst64))
+    ok = bool(np.array_equal(dst64.numpy(), D))
+    rows.append({"op": "OcTensorGPU_copy f64 dense -> f64 dense, GPU 1 -> GPU 0 (peer loads)", "us": t * 1e6, "gbs": 8 * m * m / t / 1e9,
+                 "of_plain_peer_copy": t_plain / t, "checked": ok})
+    I = rng.integers(-1000, 1001, (m, m)).astype(np.int32)
+    src32 = Tensor(torch.from_numpy(I.view(np.uint8).reshape(-1)).to("cuda:1"), "int32", [m, m], [4 * m, 4])     # transposed view
+    t = timed(lambda: ops.copy(src32, dst64))
+    ok = bool(np.array_equal(dst64.numpy(), I.astype(np.float64)))
+    plain32 = timed(lambda: raw_dst[: 4 * m * m].copy_(src32.storage[: 4 * m * m], non_blocking=True))
+    rows.append({"op": "OcTensorGPU_copy i32 4096^2 transposed on GPU 1 -> f64 dense on GPU 0 (4 bytes over the link, 8 written)",
+                 "us": t * 1e6, "link_gbs": 4 * m * m / t / 1e9, "plain_peer_copy_of_the_source_gbs": 4 * m * m / plain32 / 1e9,
+                 "of_plain_peer_copy": plain32 / t, "checked": ok})
+    print(json.dumps({"peer_copy": rows}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -791,7 +840,11 @@ def main():
     ap.add_argument("--ops-only", default=None, choices=["C1", "C2", "C3", "C4"],
                     help="run only the per-operation rows of one configuration, a few calls each, and print them "
                          "(a small case for profilers; no headline measurement)")
+    ap.add_argument("--peer-copy", action="store_true", help="time the cross-device copy between GPUs 0 and 1 (one process)")
     args = ap.parse_args()
+    if args.peer_copy:
+        run_peer_copy(args)
+        return
     if args.warmup < 3:
         args.warmup = 3
     if args.ops_only:

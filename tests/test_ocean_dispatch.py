@@ -192,7 +192,7 @@ def test_ranges_count_in_memory_order(gpu):
     kv = oc.view(k, 0)
     oc._check(oc.fn("stepsInt64")(C.byref(kv), C.c_int64(-3), C.c_int64(2)), "stepsInt64")
     assert np.array_equal(k.numpy().reshape(-1, order="F"), (-3 + 2 * np.arange(20)).astype(np.int16))
-    with pytest.raises(_ocean.OceanError, match="not supported for type"):
+    with pytest.raises(_ocean.OceanError, match="not available for type"):
         from solid_b200._lib import CDouble
         oc._check(oc.fn("stepsCDouble")(C.byref(kv), CDouble(0, 0), CDouble(1, 0)), "stepsCDouble")
 
