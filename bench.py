@@ -598,7 +598,7 @@ def run_ours(args):
     def step(i=None):
         if i is not None:
             kstart[i].record()
-        ops.axpy_sums(0.5, tx, ty, tz, sums)                 # ONE launch: streaming kernel, the folds ride in its last blocks
+        ops.axpy_sums(0.5, tx, ty, tz, sums)                 # streaming kernel + one launch that folds its partial sums
         if i is not None:
             kstop[i].record()
         shard.combine(sums, "sum")                           # per-GPU {sum z, sum z^2} added over NVLink (NCCL all-reduce)
@@ -619,6 +619,7 @@ def run_ours(args):
         for i in range(args.steps):
             step(i)
         stop.record()
+        final_dev = sums.clone()                              # {sum, norm2} of the last timed step
         barrier()
         # keep the GPU under the same load until a few more samples exist.  The loop is bounded by the clock, so its
         # trip count differs between ranks: it must not contain a collective (the kernel alone is the load).
@@ -629,7 +630,7 @@ def run_ours(args):
         barrier()
     ms_total = start.elapsed_time(stop)
     kernel_ms = sum(a.elapsed_time(b) for a, b in zip(kstart, kstop)) / args.steps
-    final = sums.cpu().numpy().tolist()
+    final = final_dev.cpu().numpy().tolist()
 
     # ---- end to end: inputs streamed from pinned host memory, result scalars read back
     win = min(n, 1 << 26)                                     # 256 MiB windows, double buffered
@@ -746,8 +747,8 @@ def run_ours(args):
                             "scalars are read back and compared with a float64 evaluation of what was streamed "
                             "(`checked`).  h2d_gbs_per_rank_bare is the same two buffers copied with nothing else "
                             "running on the rank, all ranks at once: the ceiling this number can reach."},
-            # per step: the streaming kernel (its last blocks fold the partial sums) and the square root
-            "gpu_launches": 2 * args.steps * world,
+            # per step: the streaming kernel, the fold of its partial sums, the square root
+            "gpu_launches": 3 * args.steps * world,
             "clocks": cl,
         }
         if world == 1 and not args.no_cpu:
