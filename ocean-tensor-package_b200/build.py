@@ -37,7 +37,7 @@ SINGLE_UNITS = ["base", "luts", "reduce_plan", "fused", "noalloc", "index", "gem
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--fmad=false",            # one rounding per operation, as the CPU oracle computes
               "-Xfatbin", "-compress-all",
-              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",
+              "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=default",   # exports are narrowed at link time
               "-I%s" % INCLUDE, "-I%s" % CSRC]
 
 
@@ -99,7 +99,9 @@ def build(jobs_n: int | None = None, force: bool = False, types=None, verbose: b
             if did and verbose:
                 print("[build] %-28s %6.1fs" % (obj.name, secs), flush=True)
     if rebuilt or not LIB.exists() or set(types) != set(TYPES):
-        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objects), "-lcudart"]
+        # only the C-ABI is exported (csrc/solid_exports.map); template instantiations stay local
+        cmd = [nvcc(), "-shared", "-o", str(LIB), *map(str, objects), "-lcudart",
+               "-Xlinker", "--version-script=%s" % (CSRC / "solid_exports.map")]
         res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if res.returncode != 0:
             raise RuntimeError("link failed:\n" + res.stdout)
@@ -109,7 +111,8 @@ def build(jobs_n: int | None = None, force: bool = False, types=None, verbose: b
     obj, secs, did = _compile((CSRC / "ocean_gpu.cu", BUILD / "ocean_gpu.o", []), stamp, force)
     if did or rebuilt or not OCEAN_LIB.exists():
         cmd = [nvcc(), "-shared", "-o", str(OCEAN_LIB), str(obj), "-L%s" % LIBDIR, "-lsolid_core_gpu",
-               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart"]
+               "-Xlinker", "-rpath", "-Xlinker", "$ORIGIN", "-lcudart",
+               "-Xlinker", "--version-script=%s" % (CSRC / "ocean_exports.map")]
         res = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if res.returncode != 0:
             raise RuntimeError("link failed:\n" + res.stdout)

@@ -19,7 +19,12 @@
 //
 // The first call on a device looks up the device address of the array (the array's name is a
 // host-side handle in host code, not an address a kernel could use).  Make that first call
-// before any stream capture begins.
+// before any stream capture begins.  First calls do two more one-time things that a restricted
+// context may not tolerate, so make them outside it as well: the CUDA runtime loads each kernel
+// the first time it is launched, and a reduction to a SINGLE output registers the stream it runs
+// on in a fixed table of the library (a lock and one table entry, no allocation) the first time
+// it sees that stream.  The table of resolved addresses is written without a lock: every thread
+// would store the same value.
 #include "solid_core_gpu.h"
 #include "reduce.cuh"
 #include "ops_reduce.cuh"

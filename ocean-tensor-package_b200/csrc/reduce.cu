@@ -5,7 +5,9 @@
 // solid/src/core/gpu/template_reduce_axis.cu:54-350.
 //
 // Contract kept from the reference: `result` is a HOST pointer that holds the
-// value when the call returns (one stream synchronisation), `buffer` is device
+// value when the call returns (the kernel writes it into a pinned, device-mapped
+// slot which the host polls briefly before it falls back to a stream
+// synchronisation), `buffer` is device
 // scratch of solid_gpu_reduce_all_buffer_size() bytes, empty tensors yield the
 // identity (sum 0, prod 1, any 0, all 1) and are an error for minimum/maximum.
 // Not kept: the range tests read BOTH bounds (the reference's GPU wrapper copies

@@ -17,9 +17,12 @@
 //   red_fin   when the reduced range of an output was split over several blocks
 //             (few outputs, e.g. the global case) the blocks write partial
 //             accumulators to scratch memory and this second pass folds them in
-//             index order and applies the finalize step.  There is no atomic and
-//             no inter-block wait, so results are bit-reproducible for a given
-//             device and shape.
+//             index order and applies the finalize step.  With a SINGLE output the
+//             second pass rides in red_row itself: every block counts its arrival on
+//             the stream's counter (one atomicAdd, nothing waits on it) and the block
+//             that arrives last does the same ordered fold.  The atomic only decides
+//             WHICH block folds, never the order, so results are bit-reproducible for a
+//             given device and shape.
 //
 // HBM traffic: every input element is read once; partials are a few KB.
 #pragma once
@@ -485,14 +488,16 @@ int red_launch(const R &r, RedParams p, uint32_t split_cap, cudaStream_t stream)
    // Splitting aims at one resident wave: blocks per multiprocessor that the chosen kernel can hold (asked of
    // the runtime once per kernel), never more than the RED_WANT_PER_SM that sized the scratch buffer.
    uint64_t want = (uint64_t)dev.sms * RED_WANT_PER_SM;
-   auto resident = [&](auto kernel, int &cache) {
-      if (cache == 0) {
+   // (cached per kernel AND per device: a host may hold different GPUs; a racing first call stores the same value)
+   auto resident = [&](auto kernel, int (&cache)[64]) {
+      int &slot = cache[(dev.device >= 0 && dev.device < 64) ? dev.device : 0];
+      if (slot == 0) {
          int n = 0;
          if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, RED_THREADS, 0) != cudaSuccess) { (void)cudaGetLastError(); n = 0; }
-         cache = n < 1 ? 1 : (n > RED_WANT_PER_SM ? RED_WANT_PER_SM : n);
+         slot = n < 1 ? 1 : (n > RED_WANT_PER_SM ? RED_WANT_PER_SM : n);
       }
-      want = (uint64_t)dev.sms * cache; };
-   static int occ_row_v = 0, occ_row_s = 0, occ_col_v = 0, occ_col_s = 0;
+      want = (uint64_t)dev.sms * slot; };
+   static int occ_row_v[64] = { 0 }, occ_row_s[64] = { 0 }, occ_col_v[64] = { 0 }, occ_col_s[64] = { 0 };
    auto pick_split = [&](uint64_t units) {                       // units: blocks the launch has without splitting
       uint64_t s = (want + units / 2) / units; if (s < 1) s = 1;
       if (s > split_cap) s = split_cap; return (uint32_t)s; };

@@ -4,7 +4,6 @@
 // solid/src/core/gpu/op/reduce_axis.c:22-315 (solid_gpu_reduce_axis_prepare).
 #include <cstring>
 #include <mutex>
-#include <unordered_map>
 #include "solid_core_gpu.h"
 #include "reduce.cuh"
 
@@ -46,7 +45,9 @@ __device__ unsigned int red_ticket_pool[RED_TICKETS];
 
 unsigned int *red_ticket_for_stream(cudaStream_t stream)
 {
-   struct PerDevice { unsigned int *base = nullptr; std::unordered_map<cudaStream_t, int> index; };
+   // fixed tables, no container: a call from a context that must not allocate (the no-alloc entry point) takes the
+   // lock and at most writes one table entry
+   struct PerDevice { unsigned int *base; int used; cudaStream_t streams[RED_TICKETS]; };
    static PerDevice table[64];
    static std::mutex lock;
    if (stream == cudaStreamPerThread) return nullptr;       // one handle, a different stream in every host thread
@@ -60,12 +61,10 @@ unsigned int *red_ticket_for_stream(cudaStream_t stream)
       if (cudaGetSymbolAddress(&p, red_ticket_pool) != cudaSuccess) { (void)cudaGetLastError(); return nullptr; }
       t.base = (unsigned int *)p;
    }
-   auto it = t.index.find(stream);
-   if (it != t.index.end()) return t.base + it->second;
-   if ((int)t.index.size() >= RED_TICKETS) return nullptr;
-   const int idx = (int)t.index.size();
-   t.index.emplace(stream, idx);
-   return t.base + idx;
+   for (int i = 0; i < t.used; i++) if (t.streams[i] == stream) return t.base + i;
+   if (t.used >= RED_TICKETS) return nullptr;               // table full: the caller falls back to the two-pass form
+   t.streams[t.used] = stream;
+   return t.base + t.used++;
 }
 } // namespace sd
 

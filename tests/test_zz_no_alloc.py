@@ -21,7 +21,8 @@ pytestmark = pytest.mark.gpu
 CASES = [((4096, 64), (0,)),       # dense axis: one warp or block per output, no scratch needed
          ((64, 4096), (1,)),       # strided axis, few outputs: the reduced range is split over blocks -> scratch
          ((8192, 8), (0,)),        # few outputs, long dense rows: split over blocks -> scratch
-         ((5, 6, 7), (0, 2))]
+         ((5, 6, 7), (0, 2)),
+         ((1 << 20,), (0,))]       # ONE output split over a wave of blocks: the last block to arrive folds the partials
 
 
 def run_pair(gpu, dev, shape, axes, seed):
