@@ -5,8 +5,10 @@ offset, padded, transposed, broadcast, reversed, scalar and in-place layouts.
 Tolerances: bit-exact for bool/integer results and for IEEE operations (add,
 subtract, multiply, divide, sqrt, min/max, rounding, sign, conj, ...); at most
 2 ulp for the transcendental functions named by the benchmark configurations
-(exp, log, sin and relatives on real types) and 8 ulp for the remaining
-library functions, whose GPU and glibc implementations are different programs.
+(exp, log, sin and relatives on real types) and 4 ulp for the remaining
+library functions, whose GPU and glibc implementations are different programs
+(tests/test_gpu_ulp.py measures each side against the true value: both stay
+within 1-3.5 ulp of it and within 3 ulp of each other).
 """
 import zlib
 
@@ -39,7 +41,7 @@ def unary_tolerance(op, dtype):
         return -64                                     # compositions of several library functions: see below
     if op in EXACT_UNARY:
         return 0
-    return 2 if op in ULP2_UNARY else 8
+    return 2 if op in ULP2_UNARY else 4          # measured distance between the two sides: at most 3 (test_gpu_ulp.py)
 
 
 def assert_complex_close(got, want, dtype, units, what):

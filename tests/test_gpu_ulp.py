@@ -5,8 +5,8 @@ goldens print five digits), so "GPU equals oracle" cannot hold bit for bit; the 
 is within a stated number of units in the last place of the correctly rounded result.  This test measures both on
 2^20 seeded inputs per function and element type over the function's own domain, against an evaluation with more
 precision (float64 for float results, x87 extended precision -- 64-bit mantissa -- for double results), asserts the
-bounds below and prints the table.  The tolerances of test_gpu_elemwise.py::unary_tolerance are the sum of the two
-bounds of a function, rounded up.
+bounds below and prints the table; it also asserts that the two sides are never more than three units apart, which
+is what the tolerances of test_gpu_elemwise.py::unary_tolerance (2 and 4 units) rest on.
 """
 import numpy as np
 import pytest
@@ -26,22 +26,38 @@ FUNCTIONS = {
     "arccosh": (np.arccosh, 1.001, 100.0, False), "arctanh": (np.arctanh, -0.999, 0.999, False),
     "sqrt": (np.sqrt, 1e-3, 1e3, True), "cbrt": (np.cbrt, 1e-3, 1e3, True),
     "exp": (np.exp, -20.0, 20.0, False), "exp2": (np.exp2, -30.0, 30.0, False),
-    "exp10": (lambda x: np.power(x.dtype.type(10), x), -8.0, 8.0, False), "expm1": (np.expm1, -5.0, 5.0, False),
+    "exp10": (lambda x: np.exp(x * np.log(x.dtype.type(10))), -8.0, 8.0, False), "expm1": (np.expm1, -5.0, 5.0, False),
     "log": (np.log, 1e-3, 1e3, True), "log2": (np.log2, 1e-3, 1e3, True), "log10": (np.log10, 1e-3, 1e3, True),
     "log1p": (np.log1p, -0.9, 10.0, False), "reciprocal": (lambda x: 1 / x, 1e-3, 1e3, True),
 }
 
-# Largest error, in units in the last place of the result type, that each side may show: (GPU, oracle).
-# The float bounds follow the CUDA math library's documented maxima and what glibc 2.39 measures here; anything
-# not listed is held to (2, 1).  The measured values are printed by the test.
+# Largest error, in units in the last place of the result type, that each side may show: (GPU, oracle).  Set from
+# the measurement this test prints (B200, CUDA 12.9 math library; glibc 2.39), with a quarter of headroom; anything not
+# listed is held to (2, 1).  exp10 is far from the true value on BOTH sides by construction: the reference's CPU code
+# evaluates it as exp(ln 10 * x) in the element type (solid/include/solid/core/cpu/unary_ops_cpu.h:48,93), whose
+# argument rounding alone costs up to |x| ln 10 units; the GPU code uses the same formula for the sake of parity
+# (the two sides differ by at most 2 units from each other).
+#   measured, float:  arccos 1.33/0.88  arccosh 1.49/1.65  arcsin 1.34/0.90  arcsinh 1.56/1.48  arctan 1.12/0.79
+#     arctanh 2.76/1.66  cbrt 1.12/0.94  cos 1.46/0.56  cosh 2.23/1.01  exp 1.90/0.50  exp10 20.96/20.24  exp2 2.03/0.50
+#     expm1 1.31/0.76  log 0.86/0.80  log10 2.02/1.94  log1p 0.87/0.77  log2 0.89/0.75  reciprocal 0.50/0.50
+#     sin 1.46/0.56  sinh 2.76/1.79  sqrt 0.50/0.50  tan 2.93/0.84  tanh 1.79/2.09;   GPU against oracle: at most 3
+#   measured, double: arccos 1.46/0.52  arccosh 1.86/1.69  arcsin 1.92/0.51  arcsinh 1.88/1.51  arctan 1.54/0.51
+#     arctanh 1.98/1.63  cbrt 0.50/3.23  cos 1.46/0.52  cosh 1.34/1.01  exp 0.85/0.51  exp10 31.4/31.4  exp2 0.87/0.51
+#     expm1 1.12/0.83  log 0.54/0.51  log10 1.36/1.60  log1p 1.50/0.81  log2 1.24/0.54  reciprocal 0.50/0.50
+#     sin 1.42/0.52  sinh 1.44/1.65  sqrt 0.50/0.50  tan 1.63/0.55  tanh 1.36/2.11;   GPU against oracle: at most 3
 BOUNDS = {
-    ("tan", "float"): (4.0, 1.0), ("sinh", "float"): (3.0, 1.5), ("cosh", "float"): (2.0, 1.5), ("tanh", "float"): (2.0, 1.5),
-    ("arcsin", "float"): (2.0, 1.0), ("arccos", "float"): (2.0, 1.0), ("arcsinh", "float"): (3.0, 1.5),
-    ("arccosh", "float"): (4.0, 1.5), ("arctanh", "float"): (3.0, 1.5), ("exp10", "float"): (2.0, 2.0),
-    ("sinh", "double"): (2.0, 2.0), ("cosh", "double"): (2.0, 2.0), ("tanh", "double"): (2.0, 2.0),
-    ("arcsinh", "double"): (3.0, 2.0), ("arccosh", "double"): (3.0, 2.0), ("arctanh", "double"): (2.0, 2.0),
-    ("tan", "double"): (2.0, 1.0), ("exp10", "double"): (2.0, 2.0), ("cbrt", "double"): (1.0, 4.0e6),
+    ("arccosh", "float"): (2.0, 2.0), ("arcsinh", "float"): (2.0, 2.0), ("arctanh", "float"): (3.5, 2.0),
+    ("cosh", "float"): (3.0, 1.5), ("exp", "float"): (2.5, 1.0), ("exp2", "float"): (2.5, 1.0), ("exp10", "float"): (26.0, 26.0),
+    ("log10", "float"): (2.5, 2.5), ("sinh", "float"): (3.5, 2.5), ("tan", "float"): (4.0, 1.0), ("tanh", "float"): (2.5, 2.5),
+    ("reciprocal", "float"): (1.0, 1.0), ("sqrt", "float"): (1.0, 1.0),
+    ("arccosh", "double"): (2.5, 2.0), ("arcsin", "double"): (2.5, 1.0), ("arcsinh", "double"): (2.5, 2.0),
+    ("arctanh", "double"): (2.5, 2.0), ("cbrt", "double"): (1.0, 4.0), ("cosh", "double"): (2.0, 1.5),
+    ("exp10", "double"): (40.0, 40.0), ("log10", "double"): (2.0, 2.0), ("sinh", "double"): (2.0, 2.0),
+    ("tanh", "double"): (2.0, 2.5), ("reciprocal", "double"): (1.0, 1.0), ("sqrt", "double"): (1.0, 1.0),
 }
+# Largest distance between the two sides that the measurement may show (the layout sweeps of test_gpu_elemwise.py
+# allow 2 for the functions of the benchmark configurations and 4 for the rest).
+BETWEEN = 3
 
 
 def inputs(lo, hi, logu, npdt, seed):
@@ -86,8 +102,8 @@ def test_each_side_is_within_its_bound_of_the_true_value(dtype, gpu, cpu):
             between = int(util.ulp_distance(got, want, dtype).max())
             b_gpu, b_cpu = BOUNDS.get((op, dtype), (2.0, 1.0))
             table.append((op, e_gpu, e_cpu, between, b_gpu, b_cpu))
-            if e_gpu > b_gpu or e_cpu > b_cpu:
-                failures.append((op, e_gpu, b_gpu, e_cpu, b_cpu))
+            if e_gpu > b_gpu or e_cpu > b_cpu or between > BETWEEN:
+                failures.append((op, e_gpu, b_gpu, e_cpu, b_cpu, between))
     finally:
         cpu.set_threads(1)
     print("\nmax error in ulp of %s over %d inputs per function: GPU, oracle (glibc), GPU against oracle" % (dtype, N))
