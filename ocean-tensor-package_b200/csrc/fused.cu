@@ -214,6 +214,8 @@ struct MixParams {
    uint32_t staged;             // bit k: operand k goes through the shared-memory tile
    uint64_t nelem;
    uint64_t tiles0, tilest;
+   FastDiv  div_tiles0, div_tilest;   // the grid has fewer than 2^31 blocks, so both counts fit 32 bits
+   int      anyunal;            // some operand is not aligned to its component size
 };
 
 // Operand access is split in two so that a thread can issue many loads before it
@@ -370,12 +372,17 @@ template <class C> SD_D void store_as(char *p, int dtype, C v, bool swap, bool u
 #define MIX_M0 32
 #define MIX_M1 64
 #define MIX_NT 256
+#ifndef MIX_BLOCKS
 #define MIX_BLOCKS 5
+#endif
 #endif
 constexpr int M0 = MIX_M0;                  // tile extent along dimension 0
 constexpr int M1 = MIX_M1;                  // tile extent along dimension dt
 constexpr int MT = MIX_NT;                  // threads of a tile
-constexpr int MR = 8;                       // elements per thread and operand
+#ifndef MIX_MR
+#define MIX_MR 8
+#endif
+constexpr int MR = MIX_MR;                  // elements per thread and operand
 static_assert(M0 * M1 == MT * MR, "tile and thread count do not match");
 constexpr int MP1 = MT / M1;                // rows of dimension 0 per pass of phase 1
 constexpr int MP2 = MT / M0;                // rows of dimension dt per pass of phase 2
@@ -407,34 +414,108 @@ __global__ void __launch_bounds__(256) mix_linear(const MixParams p)
    }
 }
 
+// Byte reversal under a run-time flag without a second copy of the code: the permutation selector is data.
+template <class S> SD_D S maybe_bswap(S x, bool swap)
+{
+   if constexpr (sizeof(S) == 1) return x;
+   else if constexpr (sizeof(S) == 2) {
+      uint16_t u; memcpy(&u, &x, 2);
+      u = (uint16_t)__byte_perm((uint32_t)u, 0u, swap ? 0x3201u : 0x3210u);
+      memcpy(&x, &u, 2); return x;
+   } else if constexpr (sizeof(S) == 4) {
+      uint32_t u; memcpy(&u, &x, 4);
+      u = __byte_perm(u, 0u, swap ? 0x0123u : 0x3210u);
+      memcpy(&x, &u, 4); return x;
+   } else {
+      uint64_t u; memcpy(&u, &x, 8);
+      const uint32_t lo = (uint32_t)u, hi = (uint32_t)(u >> 32), sel = swap ? 0x0123u : 0x3210u;
+      u = (uint64_t)__byte_perm(swap ? hi : lo, 0u, sel) | ((uint64_t)__byte_perm(swap ? lo : hi, 0u, sel) << 32);
+      memcpy(&x, &u, 8); return x;
+   }
+}
+// N aligned elements of storage type S (the real part where the operand is complex) as compute type C: native-width
+// loads, all issued before the first conversion.
+template <class C, class S, int N> SD_D void load_typed_n(const char *q, int64_t step, bool swap, C (&out)[N])
+{
+   S x[N];
+#pragma unroll
+   for (int j = 0; j < N; j++, q += step) x[j] = ld_one<S>(q);
+   // (a branch on the uniform flag instead of the selects of the 8-byte case was measured: 59.7 against 54.3 us)
+#pragma unroll
+   for (int j = 0; j < N; j++) out[j] = convert<C>(maybe_bswap(x[j], swap));
+}
+template <class C, int N> SD_D void load_as_n(const char *q, int64_t step, int dtype, bool swap, C (&out)[N])
+{
+   switch (dtype) {
+      case 0:  load_typed_n<C, Bool, N>(q, step, swap, out); break;
+      case 1:  load_typed_n<C, uint8_t, N>(q, step, swap, out); break;
+      case 2:  load_typed_n<C, uint16_t, N>(q, step, swap, out); break;
+      case 3:  load_typed_n<C, uint32_t, N>(q, step, swap, out); break;
+      case 4:  load_typed_n<C, uint64_t, N>(q, step, swap, out); break;
+      case 5:  load_typed_n<C, int8_t, N>(q, step, swap, out); break;
+      case 6:  load_typed_n<C, int16_t, N>(q, step, swap, out); break;
+      case 7:  load_typed_n<C, int32_t, N>(q, step, swap, out); break;
+      case 8:  load_typed_n<C, int64_t, N>(q, step, swap, out); break;
+      case 9:  case 12: load_typed_n<C, Half, N>(q, step, swap, out); break;
+      case 10: case 13: load_typed_n<C, float, N>(q, step, swap, out); break;
+      default: load_typed_n<C, double, N>(q, step, swap, out); break;
+   }
+}
+template <class C, class D, int N> SD_D void store_typed_n(char *q, int64_t step, bool swap, const C (&v)[N])
+{
+#pragma unroll
+   for (int j = 0; j < N; j++, q += step) {
+      D y = convert<D>(v[j]);
+      if constexpr (is_cplx<D>) { y.re = maybe_bswap(y.re, swap); y.im = maybe_bswap(y.im, swap); }
+      else y = maybe_bswap(y, swap);
+      st_one<D>(q, y);
+   }
+}
+template <class C, int N> SD_D void store_aligned_n(char *q, int64_t step, int dtype, bool swap, const C (&v)[N])
+{
+   switch (dtype) {
+      case 0:  store_typed_n<C, Bool, N>(q, step, swap, v); break;
+      case 1:  store_typed_n<C, uint8_t, N>(q, step, swap, v); break;
+      case 2:  store_typed_n<C, uint16_t, N>(q, step, swap, v); break;
+      case 3:  store_typed_n<C, uint32_t, N>(q, step, swap, v); break;
+      case 4:  store_typed_n<C, uint64_t, N>(q, step, swap, v); break;
+      case 5:  store_typed_n<C, int8_t, N>(q, step, swap, v); break;
+      case 6:  store_typed_n<C, int16_t, N>(q, step, swap, v); break;
+      case 7:  store_typed_n<C, int32_t, N>(q, step, swap, v); break;
+      case 8:  store_typed_n<C, int64_t, N>(q, step, swap, v); break;
+      case 9:  store_typed_n<C, Half, N>(q, step, swap, v); break;
+      case 10: store_typed_n<C, float, N>(q, step, swap, v); break;
+      case 11: store_typed_n<C, double, N>(q, step, swap, v); break;
+      case 12: store_typed_n<C, CHalf, N>(q, step, swap, v); break;
+      case 13: store_typed_n<C, CFloat, N>(q, step, swap, v); break;
+      default: store_typed_n<C, CDouble, N>(q, step, swap, v); break;
+   }
+}
+
 // Tiled variant for two or more dimensions: a tile of 32 (dimension 0) x 64 (dimension dt)
 // elements, 256 threads, 8 elements per thread and operand.  Operands that are dense along dt
 // (a transposed matrix) are first read with 64 lanes running along dt, converted and parked in
 // shared memory; then 32 lanes run along dimension 0, the remaining operands are read
-// directly (coalesced) and the result is stored.  In both phases a thread issues all loads of
-// an operand before it consumes any of them.
-template <class C, bool FULL>
-SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t (&off)[4],
-                        int64_t i0, int64_t it, int64_t n0, int64_t nt)
+// directly (coalesced) and the result is stored.  STAGED (the set of operands that go through shared memory)
+// is a template parameter, so each operand has the code of one path only.
+//
+// Interior tiles of aligned operands, i.e. nearly all the work, take mix_tile_fast: unrolled, one type switch per
+// operand and thread around native-width loads.  Edge tiles and unaligned operands take mix_tile_slow, a rolled
+// loop over the thread's elements that is small rather than fast.  (ncu on the earlier single body, which carried
+// raw 64-bit words, bounds predicates and alignment tests through the unrolled loops: 636 instructions per thread
+// for 8 elements, issue slots 60 % busy, DRAM 43 %.)
+template <class C, int STAGED>
+SD_D void mix_tile_fast(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t (&off)[4], int64_t i0, int64_t it)
 {
-   // phase 1: 64 lanes along dt, 4 rows of dimension 0 per pass
-   if (p.staged) {
+   if constexpr (STAGED != 0) {                            // phase 1: 64 lanes along dt, 4 rows of dimension 0 per pass
       const int tx = threadIdx.x & (M1 - 1), ty = threadIdx.x / M1;
-      bool ok[MR];
-#pragma unroll
-      for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + ty + MP1 * j < n0) && (it + tx < nt));
       int slot = 0;
 #pragma unroll
       for (int k = 0; k < 3; k++) {
-         if (!(p.staged & (1u << k))) continue;
-         const char *q[MR];
-         q[0] = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt] + (i0 + ty) * p.stride[k][0];
-         const int64_t step = MP1 * p.stride[k][0];
-#pragma unroll
-         for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
-         uint64_t raw[MR]; C v[MR];
-         load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
-         bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
+         if (!(STAGED & (1 << k))) continue;
+         C v[MR];
+         load_as_n<C, MR>(p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt] + (i0 + ty) * p.stride[k][0],
+                          MP1 * p.stride[k][0], p.dtype[k], p.swap[k] != 0, v);
 #pragma unroll
          for (int j = 0; j < MR; j++) tile[slot][ty + MP1 * j][tx] = v[j];
          slot++;
@@ -443,61 +524,99 @@ SD_D void mix_tile_body(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t
    }
    // phase 2: 32 lanes along dimension 0, 8 columns of dt per pass
    const int tx = threadIdx.x & (M0 - 1), ty = threadIdx.x / M0;
-   bool ok[MR];
-#pragma unroll
-   for (int j = 0; j < MR; j++) ok[j] = FULL || ((i0 + tx < n0) && (it + ty + MP2 * j < nt));
    C acc[MR];
    int slot = 0;
 #pragma unroll
-   for (int k = 0; k < 3; k++) {                        // unrolled: k selects the arithmetic at compile time
+   for (int k = 0; k < 3; k++) {                           // unrolled: k selects the arithmetic at compile time
       C v[MR];
-      if (p.staged & (1u << k)) {
+      if (STAGED & (1 << k)) {
 #pragma unroll
          for (int j = 0; j < MR; j++) v[j] = tile[slot][tx][ty + MP2 * j];
          slot++;
       } else {
-         const char *q[MR];
-         q[0] = p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0] + (it + ty) * p.stride[k][p.dt];
-         const int64_t step = MP2 * p.stride[k][p.dt];
-#pragma unroll
-         for (int j = 1; j < MR; j++) q[j] = q[j - 1] + step;
-         uint64_t raw[MR];
-         load_bits_n<MR>(q, ok, p.comp[k], p.unal[k], raw);
-         bits_as_n<C, MR>(raw, p.dtype[k], p.swap[k], v);
+         load_as_n<C, MR>(p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0] + (it + ty) * p.stride[k][p.dt],
+                          MP2 * p.stride[k][p.dt], p.dtype[k], p.swap[k] != 0, v);
       }
 #pragma unroll
       for (int j = 0; j < MR; j++) acc[j] = (k == 0) ? v[j] : (k == 1 ? acc[j] * v[j] : acc[j] + v[j]);   // rounded product, rounded sum
    }
-   char *qo[MR];
-   qo[0] = p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0] + (it + ty) * p.stride[3][p.dt];
-   const int64_t ostep = MP2 * p.stride[3][p.dt];
-#pragma unroll
-   for (int j = 1; j < MR; j++) qo[j] = qo[j - 1] + ostep;
-   store_as_n<C, MR>(qo, ok, p.dtype[3], acc, p.swap[3], p.unal[3]);
+   store_aligned_n<C, MR>(p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0] + (it + ty) * p.stride[3][p.dt],
+                          MP2 * p.stride[3][p.dt], p.dtype[3], p.swap[3] != 0, acc);
 }
 
-template <class C>
+template <class C, int STAGED>
+SD_D void mix_tile_slow(const MixParams &p, C (*tile)[M0][M1 + 1], const int64_t (&off)[4],
+                        int64_t i0, int64_t it, int64_t n0, int64_t nt)
+{
+   if constexpr (STAGED != 0) {
+      const int tx = threadIdx.x & (M1 - 1), ty = threadIdx.x / M1;
+      int slot = 0;
+#pragma unroll
+      for (int k = 0; k < 3; k++) {
+         if (!(STAGED & (1 << k))) continue;
+         const char *q = p.ptr[k] + off[k] + (it + tx) * p.stride[k][p.dt] + (i0 + ty) * p.stride[k][0];
+#pragma unroll 1
+         for (int j = 0; j < MR; j++, q += MP1 * p.stride[k][0]) {
+            const bool ok = (i0 + ty + MP1 * j < n0) && (it + tx < nt);
+            tile[slot][ty + MP1 * j][tx] = ok ? bits_as<C>(load_bits(q, p.comp[k], p.unal[k] != 0), p.dtype[k], p.swap[k] != 0) : C(0);
+         }
+         slot++;
+      }
+      __syncthreads();
+   }
+   const int tx = threadIdx.x & (M0 - 1), ty = threadIdx.x / M0;
+   if (i0 + tx >= n0) return;
+#pragma unroll 1
+   for (int j = 0; j < MR; j++) {
+      const int64_t t = it + ty + MP2 * j;
+      if (t >= nt) break;
+      C acc = C(0);
+      int slot = 0;
+#pragma unroll
+      for (int k = 0; k < 3; k++) {
+         C v;
+         if (STAGED & (1 << k)) { v = tile[slot][tx][ty + MP2 * j]; slot++; }
+         else v = bits_as<C>(load_bits(p.ptr[k] + off[k] + (i0 + tx) * p.stride[k][0] + t * p.stride[k][p.dt], p.comp[k], p.unal[k] != 0),
+                             p.dtype[k], p.swap[k] != 0);
+         acc = (k == 0) ? v : (k == 1 ? acc * v : acc + v);
+      }
+      store_as<C>(p.ptr[3] + off[3] + (i0 + tx) * p.stride[3][0] + t * p.stride[3][p.dt], p.dtype[3], acc, p.swap[3] != 0, p.unal[3] != 0);
+   }
+}
+
+template <class C, int STAGED>
 __global__ void __launch_bounds__(MT, MIX_BLOCKS) mix_tiled(const MixParams p)
 {
    extern __shared__ __align__(16) unsigned char mix_smem[];
    C (*tile)[M0][M1 + 1] = reinterpret_cast<C (*)[M0][M1 + 1]>(mix_smem);
-   uint64_t bid = blockIdx.x;
-   uint64_t bq = udiv64(bid, p.tiles0);
-   const uint64_t t0 = bid - bq * p.tiles0; bid = bq;
-   bq = udiv64(bid, p.tilest);
-   const uint64_t tt = bid - bq * p.tilest; bid = bq;
+   uint32_t bid = blockIdx.x;
+   uint32_t bq = fastdiv(bid, p.div_tiles0);
+   const uint32_t t0 = bid - bq * (uint32_t)p.tiles0; bid = bq;
+   bq = fastdiv(bid, p.div_tilest);
+   const uint32_t tt = bid - bq * (uint32_t)p.tilest; bid = bq;
    int64_t off[4] = {0, 0, 0, 0};
    for (int d = 1; d < p.ndims; d++) {
       if (d == p.dt) continue;
-      uint64_t q = udiv64(bid, (uint64_t)p.size[d]); uint64_t c = bid - q * (uint64_t)p.size[d]; bid = q;
+      uint32_t q = bid / (uint32_t)p.size[d]; uint32_t c = bid - q * (uint32_t)p.size[d]; bid = q;   // bid < size[d] * (the rest) < 2^31
 #pragma unroll
       for (int k = 0; k < 4; k++) off[k] += (int64_t)c * p.stride[k][d];
    }
    const int64_t i0 = (int64_t)t0 * M0, it = (int64_t)tt * M1;
    const int64_t n0 = p.size[0], nt = p.size[p.dt];
-   // interior tiles take the copy of the body without bounds predicates
-   if (i0 + M0 <= n0 && it + M1 <= nt) mix_tile_body<C, true>(p, tile, off, i0, it, n0, nt);
-   else                                mix_tile_body<C, false>(p, tile, off, i0, it, n0, nt);
+   if (i0 + M0 <= n0 && it + M1 <= nt && !p.anyunal) mix_tile_fast<C, STAGED>(p, tile, off, i0, it);
+   else                                              mix_tile_slow<C, STAGED>(p, tile, off, i0, it, n0, nt);
+}
+
+template <class C, int STAGED>
+int mix_tiled_launch(const MixParams &p, uint64_t blocks, size_t smem, cudaStream_t stream)
+{
+   static bool attr_set = false;
+   if (smem > 48 * 1024 && !attr_set) {
+      SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C, STAGED>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * M0 * (M1 + 1) * (int)sizeof(C)));
+      attr_set = true;
+   }
+   mix_tiled<C, STAGED><<<(unsigned)blocks, MT, smem, stream>>>(p);
+   return 0;
 }
 
 template <class C>
@@ -548,12 +667,20 @@ int mixed_multiply_add(int ndims, const size_t *size, const solid_gpu_operand *c
       int nstaged = 0;
       for (int k = 0; k < 3; k++) if (staged & (1u << k)) nstaged++;
       size_t smem = (size_t)nstaged * M0 * (M1 + 1) * sizeof(C);            // up to 3 x 16.3 KB
-      static bool attr_set[2] = { false, false };
-      if (smem > 48 * 1024 && !attr_set[sizeof(C) == 8]) {
-         SD_CUDA_CHECK(cudaFuncSetAttribute(mix_tiled<C>, cudaFuncAttributeMaxDynamicSharedMemorySize, 3 * M0 * (M1 + 1) * (int)sizeof(C)));
-         attr_set[sizeof(C) == 8] = true;
+      p.div_tiles0 = make_fastdiv((uint32_t)p.tiles0); p.div_tilest = make_fastdiv((uint32_t)p.tilest);
+      p.anyunal = (p.unal[0] | p.unal[1] | p.unal[2] | p.unal[3]) ? 1 : 0;
+      int rc = 0;
+      switch (staged) {                                              // one kernel per set of staged operands
+         case 0: rc = mix_tiled_launch<C, 0>(p, blocks, smem, stream); break;
+         case 1: rc = mix_tiled_launch<C, 1>(p, blocks, smem, stream); break;
+         case 2: rc = mix_tiled_launch<C, 2>(p, blocks, smem, stream); break;
+         case 3: rc = mix_tiled_launch<C, 3>(p, blocks, smem, stream); break;
+         case 4: rc = mix_tiled_launch<C, 4>(p, blocks, smem, stream); break;
+         case 5: rc = mix_tiled_launch<C, 5>(p, blocks, smem, stream); break;
+         case 6: rc = mix_tiled_launch<C, 6>(p, blocks, smem, stream); break;
+         default: rc = mix_tiled_launch<C, 7>(p, blocks, smem, stream); break;
       }
-      mix_tiled<C><<<(unsigned)blocks, MT, smem, stream>>>(p);
+      if (rc != 0) return rc;
    } else {
       uint64_t blocks = (p.nelem + 256ull * MR - 1) / (256ull * MR);
       if (blocks > 0x7FFFFFFFull) blocks = 0x7FFFFFFFull;            // one chunk per block

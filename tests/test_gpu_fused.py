@@ -38,13 +38,22 @@ def test_mixed_multiply_add_matches_reference_sequence(case, gpu, cpu):
     ctype, dst, (ta, sa), (tb, sb), (tc, sc) = case
     dev = util.Device()
     rng = np.random.default_rng(5)
+    # (130, 70) and (96, 192) hold interior tiles (the unrolled path) as well as edge tiles; "swapped_dst" stores the
+    # result with reversed bytes; the 3-d case keeps a third dimension that cannot be merged (padded planes)
     for shape, layout in (((130, 70), "transposed_a"), ((64, 64), "dense"), ((33, 17, 3), "dense"),
-                          ((4099,), "dense"), ((96, 40), "broadcast_c"), ((70, 50), "unaligned_b")):
+                          ((4099,), "dense"), ((96, 40), "broadcast_c"), ((70, 50), "unaligned_b"),
+                          ((96, 192), "transposed_a swapped_dst"), ((70, 130, 3), "transposed_a planes"),
+                          ((64, 128), "dense_2d_padded swapped_dst")):
         n = int(np.prod(shape))
+        sd = "swapped_dst" in layout
         # views
-        if layout == "transposed_a" and len(shape) == 2:
-            base = util.dense_view(ta, [shape[1], shape[0]])
-            va = util.View(ta, list(shape), [base.strides[1], base.strides[0]], 0, base.nbytes)
+        if "transposed_a" in layout:
+            es_a = dt.SIZE[ta]
+            if len(shape) == 2:
+                va = util.View(ta, list(shape), [shape[1] * es_a, es_a], 0, n * es_a)
+            else:                                    # planes of transposed matrices, 5 elements of padding between planes
+                plane = (shape[0] * shape[1] + 5) * es_a
+                va = util.View(ta, list(shape), [shape[1] * es_a, es_a, plane], 0, plane * shape[2])
         else:
             va = util.dense_view(ta, list(shape))
         vb = util.dense_view(tb, list(shape), pad_elems=3 if len(shape) > 1 else 0)
@@ -55,7 +64,7 @@ def test_mixed_multiply_add_matches_reference_sequence(case, gpu, cpu):
             vc = util.View(tc, list(shape), [0, dt.SIZE[tc]], 0, shape[1] * dt.SIZE[tc] + 64)
         else:
             vc = util.dense_view(tc, list(shape))
-        vd = util.dense_view(dst, list(shape))
+        vd = util.dense_view(dst, list(shape), pad_elems=2 if "padded" in layout else 0)
         kind = "small" if (dst in dt.GROUPS["integer"] or ta in dt.SINT) else "general"
         bufs = []
         for v, sw in ((va, sa), (vb, sb), (vc, sc)):
@@ -72,16 +81,31 @@ def test_mixed_multiply_add_matches_reference_sequence(case, gpu, cpu):
         P, S = np.zeros(n, dtype=dt.NUMPY[ctype]), np.zeros(n, dtype=dt.NUMPY[ctype])
         cpu.binary("multiply", ctype, [n], [es], A.ctypes.data, [es], B.ctypes.data, [es], P.ctypes.data)
         cpu.binary("add", ctype, [n], [es], P.ctypes.data, [es], Cc.ctypes.data, [es], S.ctypes.data)
-        want = np.zeros(vd.nbytes, dtype=np.uint8)
+        want = np.zeros(n * dt.SIZE[dst], dtype=np.uint8)
         cpu.copy(ctype, dst, [n], [es], S.ctypes.data, [n], [dt.SIZE[dst]], want.ctypes.data)
+        if sd:
+            from test_gpu_copy import swap_buffer
+            want = swap_buffer(want, dst, util.dense_view(dst, [n]))
         # fused kernel
         d = [dev.upload(b) for b in bufs]
         dd = dev.upload(np.zeros(vd.nbytes, dtype=np.uint8))
         gpu.mixed_multiply_add(list(shape), [(d[0].data_ptr() + va.offset, va.strides, ta, sa),
                                              (d[1].data_ptr() + vb.offset, vb.strides, tb, sb),
                                              (d[2].data_ptr() + vc.offset, vc.strides, tc, sc),
-                                             (dd.data_ptr(), vd.strides, dst, False)], ctype, dev.stream)
+                                             (dd.data_ptr(), vd.strides, dst, sd)], ctype, dev.stream)
         got = dev.download(dd)
+        elems = util.gather(got, vd)                 # column-major elements of the (possibly padded) destination
+        untouched = got.copy()
+        esd = dt.SIZE[dst]
+        idx = np.zeros(1, dtype=np.int64)
+        for sz, st in zip(vd.size, vd.strides):
+            idx = (np.arange(sz, dtype=np.int64)[:, None] * st + idx[None, :]).reshape(-1)
+        untouched[(idx[:, None] + np.arange(esd)[None, :]).reshape(-1)] = 0
+        assert not untouched.any(), "bytes outside the destination's elements were written (%s %s)" % (case, layout)
+        got = elems.view(np.uint8)
+        if sd:                                       # compare the stored bytes: NaN payloads do not arise in these cases
+            assert np.array_equal(got, want), "%s %s %s" % (case, shape, layout)
+            continue
         # same bits, except that two NaNs count as equal whatever their payload (rows of the unaligned
         # operand reinterpret neighbouring bytes, which may happen to be NaN patterns)
         g = got[: n * dt.SIZE[dst]].view(dt.NUMPY[dst]); w = want[: n * dt.SIZE[dst]].view(dt.NUMPY[dst])
