@@ -395,7 +395,21 @@ def ops_table(peak: float, with_cpu: bool, only=None, iters_scale: float = 1.0, 
         tF3 = Tensor.empty([m, m], "float")
         add_row("C2", "add f32 A^T + B 4096^2 (one operand transposed)", 12 * m * m, lambda: ops.binary("add", tF1, tF2, tF3),
                 check=lambda: same_bits(tF3.numpy().reshape(-1, order="F"), F1.reshape(-1, order="F") + F2.reshape(-1)))
-        del tA64, tB64, tr64, tr64b, trv, tP, tS, tC2, tF1, tF2, tF3
+        # strided views that are dense along dimension 0: padded rows (a 4096 x 4096 block of arrays with a pitch of
+        # 4160 elements) and an operand broadcast along dimension 0
+        pitch = m + 64
+        G1 = rng.uniform(-1, 1, (m, pitch)).astype(np.float32); G2 = rng.uniform(-1, 1, (m, pitch)).astype(np.float32)
+        tG1 = Tensor(torch.from_numpy(G1.view(np.uint8).reshape(-1)).cuda(), "float", [m, m], [4, 4 * pitch])
+        tG2 = Tensor(torch.from_numpy(G2.view(np.uint8).reshape(-1)).cuda(), "float", [m, m], [4, 4 * pitch])
+        tG3 = Tensor(torch.zeros(4 * m * pitch, dtype=torch.uint8, device="cuda"), "float", [m, m], [4, 4 * pitch])
+        add_row("C2", "add f32 on 4096^2 blocks of arrays with padded rows (pitch 4160)", 12 * m * m,
+                lambda: ops.binary("add", tG1, tG2, tG3),
+                check=lambda: same_bits(np.ascontiguousarray(tG3.storage.cpu().numpy().view(np.float32).reshape(m, pitch)[:, :m]).reshape(-1),
+                                        (G1[:, :m] + G2[:, :m]).reshape(-1)))
+        add_row("C2", "add f64 P + r 4096^2 (r broadcast along dimension 0)", 16 * m * m,
+                lambda: ops.binary("add", tP, tr64b, tS),
+                check=lambda: same_bits(tS.numpy().reshape(-1, order="F"), tP.numpy().reshape(-1, order="F") + np.repeat(tr64.numpy().reshape(-1), m)))
+        del tA64, tB64, tr64, tr64b, trv, tP, tS, tC2, tF1, tF2, tF3, tG1, tG2, tG3
         raw = np.zeros(8 * m * m + 64, dtype=np.uint8)
         raw[3: 3 + 8 * m * m] = A.astype(">f8").view(np.uint8).reshape(-1)
         tU = Tensor(torch.from_numpy(raw).cuda(), "double", [m * m], [8], offset=3, byteswapped=True)

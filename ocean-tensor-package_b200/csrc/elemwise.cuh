@@ -224,7 +224,18 @@ __global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig
 }
 
 // ---------------------------------------------------------------------------
-template <class A, int VEC, bool UNAL>
+// One position (a run of K vectors of VEC elements along dimension 0) per thread and loop pass; the grid has one
+// block per EW_THREADS positions.  K > 1 spreads the index decomposition over K vectors: with 16-byte vectors of
+// doubles (VEC = 2) one vector per thread left the kernel bound by the decomposition, not by memory (a double add
+// with a row broadcast along dimension 0 took the time of a three-operand add).  Measured on 4096^2 (B200), K = 1 / 2 /
+// 4: double add with a broadcast row 67.8 / 49.4 / 53.0 us, double add on padded rows 67.7 / 59.7 / 69.8 us, float
+// add on padded rows 35.7 / 34.8 / 42.0 us: two vectors it is (64 contiguous bytes per thread cost coalescing).
+// Measured and rejected: several POSITIONS per thread with all loads issued first (2 and 4 positions: 15 % and 35 %
+// slower on padded rows).
+#ifndef EW_STRIDED_K
+#define EW_STRIDED_K 2
+#endif
+template <class A, int VEC, int K, bool UNAL>
 __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const EwParams<A::NIN + 1> p)
 {
    using X = ew_traits<A>;
@@ -261,16 +272,23 @@ __global__ void __launch_bounds__(EW_THREADS) ew_strided(const A apply, const Ew
 #pragma unroll
          for (int k = 0; k < NOPS; k++) off[k] += (int64_t)r * p.stride[k][p.ndims - 1];
       }
-      Vec<in1_t, VEC> a; Vec<in2_t, VEC> b;
-      if constexpr (NIN >= 1) a = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + off[0], VEC > 1 && b1, u1);
-      if constexpr (NIN >= 2) b = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + off[1], VEC > 1 && b2, u2);
-      Vec<out_t, VEC> o;
-      if constexpr (has_vector_apply<A>::value && (VEC > 1)) o = apply.template vec<VEC>(a, b);
-      else {
+      // K > 1 only with VEC > 1: every operand is then dense (or broadcast) along dimension 0
+      Vec<in1_t, VEC> a[K]; Vec<in2_t, VEC> b[K];
 #pragma unroll
-         for (int j = 0; j < VEC; j++) o.v[j] = apply(a.v[j], b.v[j]);
+      for (int j = 0; j < K; j++) {
+         if constexpr (NIN >= 1) { if (j == 0 || !b1) a[j] = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + off[0] + (b1 ? 0 : j * VEC * (int)sizeof(in1_t)), VEC > 1 && b1, u1); else a[j] = a[0]; }
+         if constexpr (NIN >= 2) { if (j == 0 || !b2) b[j] = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + off[1] + (b2 ? 0 : j * VEC * (int)sizeof(in2_t)), VEC > 1 && b2, u2); else b[j] = b[0]; }
       }
-      ew_store<out_t, VEC, UNAL>(p.ptr[NIN] + off[NIN], o, uo);
+#pragma unroll
+      for (int j = 0; j < K; j++) {
+         Vec<out_t, VEC> o;
+         if constexpr (has_vector_apply<A>::value && (VEC > 1)) o = apply.template vec<VEC>(a[j], b[j]);
+         else {
+#pragma unroll
+            for (int e = 0; e < VEC; e++) o.v[e] = apply(a[j].v[e], b[j].v[e]);
+         }
+         ew_store<out_t, VEC, UNAL>(p.ptr[NIN] + off[NIN] + j * VEC * (int)sizeof(out_t), o, uo);
+      }
    }
 }
 
@@ -542,7 +560,10 @@ int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
       if ((bcast | unal) & (1u << k)) continue;
       for (int d = 1; d < L.ndims; d++) if (L.stride[k][d] % (int64_t)vec_align(k) != 0) { vec_ok = false; break; }
    }
-   const int vec = vec_ok ? VEC : 1;
+   // K consecutive vectors per thread when rows divide evenly and are long enough to keep a warp on one row
+   constexpr int K = (VEC > 1 && VEC * X::s_max * EW_STRIDED_K <= 64) ? EW_STRIDED_K : ((VEC > 1 && VEC * X::s_max * 2 <= 64) ? 2 : 1);
+   const bool run_ok = vec_ok && K > 1 && (L.size[0] % (VEC * K) == 0) && (L.size[0] / (VEC * K) >= 32);
+   const int vec = vec_ok ? (run_ok ? VEC * K : VEC) : 1;
    p.ndims = L.ndims;
    p.bcast = vec_ok ? bcast : 0;
    uint64_t total = 1; bool fits32 = true;
@@ -559,11 +580,13 @@ int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
    p.wide = (total > 0xFFFFFFFFull || !fits32) ? 1 : 0;
    int grid = ew_grid(total, EW_THREADS, dev);
    if (ALLOW_UNALIGNED && unal) {
-      if (vec_ok) ew_strided<A, VEC, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
-      else        ew_strided<A, 1, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      if (run_ok)      ew_strided<A, VEC, K, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else if (vec_ok) ew_strided<A, VEC, 1, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else             ew_strided<A, 1, 1, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
    } else {
-      if (vec_ok) ew_strided<A, VEC, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
-      else        ew_strided<A, 1, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      if (run_ok)      ew_strided<A, VEC, K, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else if (vec_ok) ew_strided<A, VEC, 1, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      else             ew_strided<A, 1, 1, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
    }
    SD_LAUNCH_CHECK();
    return 0;
