@@ -33,6 +33,10 @@ namespace sd {
 struct Nothing {};
 
 constexpr int EW_THREADS = 256;
+#ifndef EW_CONTIG_THREADS
+#define EW_CONTIG_THREADS 256
+#endif
+constexpr int EWC_THREADS = EW_CONTIG_THREADS;     // block size of the contiguous kernel
 
 template <int NOPS> struct EwParams {
    char    *ptr[NOPS];
@@ -62,8 +66,18 @@ template <class A> struct ew_traits {
    // elements per thread-iteration: 16 bytes of the narrowest operand, at most 64 of the widest
    static constexpr int VEC0 = 16 / s_min > 0 ? 16 / s_min : 1;
    static constexpr int VEC = (VEC0 * s_max > 64) ? (64 / s_max > 0 ? 64 / s_max : 1) : VEC0;
-   // independent iterations in flight: about 64 bytes per operand and thread
-   static constexpr int UNROLL = (64 / (VEC * s_max)) > 0 ? (64 / (VEC * s_max)) : 1;
+   // Independent iterations in flight, as bytes of the widest operand per thread.  Measured on B200 with arrays of
+   // 1-3 GB (256 threads, one chunk per block), 64 / 32 / 16 bytes: 4-byte elements 7.0 / 7.0 / 7.2 TB/s on add and
+   // 6.8 / 6.2 / 5.4 on sin, so 64; 8- and 16-byte elements 6.2 / 7.0 / 7.1 on add and 6.2 / 6.7 / 5.8 on fabs
+   // (the wide forms need 58-64 registers, four blocks per multiprocessor), so 32; 2-byte elements 4.0 / 6.0 / 7.2 on
+   // add and 5.6 / 6.5 / 6.0 on negative, 1-byte elements 2.0 / 3.2 / 4.8 and 3.5 / 4.6 / 4.9 (unpacking makes them
+   // instruction-bound, more warps hide it), so 16, except 32 for one-source operations on 2-byte elements.
+#ifdef EW_FLIGHT_BYTES_FORCED
+   static constexpr int FLIGHT = EW_FLIGHT_BYTES_FORCED;
+#else
+   static constexpr int FLIGHT = s_max >= 8 ? 32 : (s_max == 4 ? 64 : ((s_max == 1 || NIN == 2) ? 16 : 32));
+#endif
+   static constexpr int UNROLL = (FLIGHT / (VEC * s_max)) > 0 ? (FLIGHT / (VEC * s_max)) : 1;
 };
 
 // An apply object may provide   template <int N> Vec<out_t, N> vec(const Vec<in1_t, N> &, const Vec<in2_t, N> &) const
@@ -175,13 +189,13 @@ template <class T, int VEC, bool UNAL> SD_D void ew_store(char *p, const Vec<T, 
 
 // ---------------------------------------------------------------------------
 template <class A, bool UNAL>
-__global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig(const A apply, const EwParams<A::NIN + 1> p)
+__global__ void __launch_bounds__(EWC_THREADS, ew_min_blocks<A>::value) ew_contig(const A apply, const EwParams<A::NIN + 1> p)
 {
    using X = ew_traits<A>;
    constexpr int VEC = X::VEC, U = X::UNROLL, NIN = X::NIN;
    using out_t = typename X::out_t; using in1_t = typename X::in1_t; using in2_t = typename X::in2_t;
    const uint64_t nvec = p.nelem / VEC;
-   const uint64_t chunk = (uint64_t)EW_THREADS * U;
+   const uint64_t chunk = (uint64_t)EWC_THREADS * U;
    const bool b1 = p.bcast & 1u, b2 = p.bcast & 2u;
    const bool u1 = p.unal & 1u, u2 = p.unal & 2u, uo = p.unal & (1u << NIN);
    char *const po = p.ptr[NIN];
@@ -190,7 +204,7 @@ __global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig
       Vec<in1_t, VEC> a[U]; Vec<in2_t, VEC> b[U];
 #pragma unroll
       for (int u = 0; u < U; u++) {
-         uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
+         uint64_t i = base + (uint64_t)u * EWC_THREADS + threadIdx.x;
          if (i < nvec) {
             if constexpr (NIN >= 1) a[u] = ew_load<in1_t, VEC, UNAL>(p.ptr[0] + (b1 ? 0 : i * (VEC * sizeof(in1_t))), b1, u1);
             if constexpr (NIN >= 2) b[u] = ew_load<in2_t, VEC, UNAL>(p.ptr[1] + (b2 ? 0 : i * (VEC * sizeof(in2_t))), b2, u2);
@@ -198,7 +212,7 @@ __global__ void __launch_bounds__(EW_THREADS, ew_min_blocks<A>::value) ew_contig
       }
 #pragma unroll
       for (int u = 0; u < U; u++) {
-         uint64_t i = base + (uint64_t)u * EW_THREADS + threadIdx.x;
+         uint64_t i = base + (uint64_t)u * EWC_THREADS + threadIdx.x;
          if (i < nvec) {
             Vec<out_t, VEC> o;
             if constexpr (has_vector_apply<A>::value && (VEC > 1)) o = apply.template vec<VEC>(a[u], b[u]);
@@ -528,9 +542,9 @@ int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
    if (L.ndims == 1 && dense0 && (aligned || VEC == 1)) {
       p.bcast = bcast;
       uint64_t nvec = p.nelem / VEC;
-      int grid = ew_grid(nvec ? nvec : 1, (uint64_t)EW_THREADS * X::UNROLL, dev);
-      if (ALLOW_UNALIGNED && unal) ew_contig<A, ALLOW_UNALIGNED><<<grid, EW_THREADS, 0, stream>>>(apply, p);
-      else                         ew_contig<A, false><<<grid, EW_THREADS, 0, stream>>>(apply, p);
+      int grid = ew_grid(nvec ? nvec : 1, (uint64_t)EWC_THREADS * X::UNROLL, dev);
+      if (ALLOW_UNALIGNED && unal) ew_contig<A, ALLOW_UNALIGNED><<<grid, EWC_THREADS, 0, stream>>>(apply, p);
+      else                         ew_contig<A, false><<<grid, EWC_THREADS, 0, stream>>>(apply, p);
       SD_LAUNCH_CHECK();
       return 0;
    }
@@ -595,6 +609,59 @@ int ew_launch(const A &apply, Layout<A::NIN + 1> &L, cudaStream_t stream)
 // ---------------------------------------------------------------------------
 // Apply adaptors for the functors of ops_unary.cuh / ops_binary.cuh
 // ---------------------------------------------------------------------------
+// Operations on 8- and 16-bit integers and on bool bytes that act on each byte (or half word) independently are
+// run on whole 32-bit words whenever every operand is dense along dimension 0 with word-aligned rows: the tensors
+// are re-described as tensors of uint32 and go through the same engine (contiguous, strided, runs) as any 4-byte
+// type.  A vector of sixteen separate bytes costs the compiler some fifty registers and a pack / unpack sequence:
+// the per-element form of a contiguous uint8 and ran at 2.0-4.6 TB/s (64 to 16 bytes in flight) where a 4-byte add
+// runs at 7.0.  word_op<Op, T>::f is the operation on four packed bytes / two packed half words.
+struct b_bitwise_and; struct b_bitwise_or; struct b_bitwise_xor; struct b_add; struct b_subtract; struct b_multiply;
+struct u_negative; struct u_bitwise_not;                   // defined in ops_binary.cuh / ops_unary.cuh
+template <class Op, class T, class = void> struct word_op { static constexpr bool value = false; };
+template <class T> constexpr bool is_narrow_int = is_int<T> && sizeof(T) <= 2;
+template <class T> constexpr bool is_narrow = (is_int<T> && sizeof(T) <= 2) || is_bool<T>;
+#define SD_WORD_OP(OP, COND, EXPR)                                                                   \
+   template <class T> struct word_op<OP, T, std::enable_if_t<(COND)>> {                               \
+      static constexpr bool value = true;                                                            \
+      static SD_D uint32_t f(uint32_t a, uint32_t b) { (void)b; return (EXPR); } };
+SD_WORD_OP(b_bitwise_and, is_narrow<T>, a & b)
+SD_WORD_OP(b_bitwise_or,  is_narrow<T>, a | b)
+SD_WORD_OP(b_bitwise_xor, is_narrow<T>, a ^ b)
+SD_WORD_OP(b_add,      is_narrow_int<T>, sizeof(T) == 1 ? __vadd4(a, b) : __vadd2(a, b))      // wrap-around per element
+SD_WORD_OP(b_subtract, is_narrow_int<T>, sizeof(T) == 1 ? __vsub4(a, b) : __vsub2(a, b))
+SD_WORD_OP(b_add,      is_bool<T>, a | b)                                                      // the bool aliases
+SD_WORD_OP(b_subtract, is_bool<T>, a & ~b)
+SD_WORD_OP(b_multiply, is_bool<T>, a & b)
+SD_WORD_OP(u_negative,    is_narrow_int<T>, sizeof(T) == 1 ? __vneg4(a) : __vneg2(a))
+SD_WORD_OP(u_negative,    is_bool<T>, a ^ 0x01010101u)
+SD_WORD_OP(u_bitwise_not, is_narrow_int<T>, ~a)
+SD_WORD_OP(u_bitwise_not, is_bool<T>, a ^ 0x01010101u)
+#undef SD_WORD_OP
+template <class Op, class T> struct WordUnaryApply {
+   static constexpr int NIN = 1;
+   using in1_t = uint32_t; using in2_t = Nothing; using out_t = uint32_t;
+   SD_D uint32_t operator()(uint32_t x, Nothing) const { return word_op<Op, T>::f(x, x); }
+};
+template <class Op, class T> struct WordBinaryApply {
+   static constexpr int NIN = 2;
+   using in1_t = uint32_t; using in2_t = uint32_t; using out_t = uint32_t;
+   SD_D uint32_t operator()(uint32_t x, uint32_t y) const { return word_op<Op, T>::f(x, y); }
+};
+// Re-describe operands of `es`-byte elements as words; false (layout untouched) when some operand is not made of
+// whole aligned words along dimension 0.
+template <int NOPS> inline bool layout_as_words(Layout<NOPS> &L, int es)
+{
+   const int per = 4 / es;
+   if (L.nelem == 0 || L.ndims < 1 || L.size[0] % per != 0) return false;
+   for (int k = 0; k < NOPS; k++) {
+      if (L.stride[k][0] != es || !aligned_to(L.ptr[k], 4)) return false;
+      for (int d = 1; d < L.ndims; d++) if (L.stride[k][d] % 4 != 0) return false;
+   }
+   L.size[0] /= per; L.nelem /= per;
+   for (int k = 0; k < NOPS; k++) L.stride[k][0] = 4;
+   return true;
+}
+
 template <class Op, class T> struct UnaryApply {
    static constexpr int NIN = 1;
    using in1_t = T; using in2_t = Nothing; using out_t = typename Op::template out<T>;
@@ -614,6 +681,7 @@ int launch_unary(int ndims, const size_t *size, const ptrdiff_t *strides1, void 
    const ptrdiff_t *st[2] = { strides1, strides2 }; void *pt[2] = { ptr1, ptr2 };
    Layout<2> L;
    if (make_layout<2>(L, ndims, size, st, pt, 1) != 0) return -1;
+   if constexpr (word_op<Op, T>::value) { if (layout_as_words<2>(L, (int)sizeof(T))) return ew_launch(WordUnaryApply<Op, T>(), L, stream); }
    return ew_launch(UnaryApply<Op, T>(), L, stream);
 }
 
@@ -626,6 +694,7 @@ int launch_binary(int ndims, const size_t *size, const ptrdiff_t *strides1, void
    const ptrdiff_t *st[3] = { strides1, strides2, strides3 }; void *pt[3] = { ptr1, ptr2, ptr3 };
    Layout<3> L;
    if (make_layout<3>(L, ndims, size, st, pt, 2) != 0) return -1;
+   if constexpr (word_op<Op, T>::value) { if (layout_as_words<3>(L, (int)sizeof(T))) return ew_launch(WordBinaryApply<Op, T>(), L, stream); }
    return ew_launch(BinaryApply<Op, T>(), L, stream);
 }
 
