@@ -609,14 +609,21 @@ def run_ours(args):
     kstart = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
     kstop = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
 
+    # The exchange of the per-GPU pairs: one kernel of the library over peer memory (NVLink) where symmetric memory can
+    # be set up, else the NCCL all-reduce followed by the square root (SOLID_B200_EXCHANGE=nccl forces the latter).
+    peer = shard.PeerSum.create(device) if world > 1 else None
+
     def step(i=None):
         if i is not None:
             kstart[i].record()
         ops.axpy_sums(0.5, tx, ty, tz, sums)                 # streaming kernel + one launch that folds its partial sums
         if i is not None:
             kstop[i].record()
-        shard.combine(sums, "sum")                           # per-GPU {sum z, sum z^2} added over NVLink (NCCL all-reduce)
-        ops.unary("sqrt", t_sumsq, t_sumsq)                  # norm2 in place, one small launch of the library
+        if peer is not None:
+            peer.sum_pair(sums, sqrt_second=True)            # pairs exchanged through peer memory, added in rank order, norm2
+        else:
+            shard.combine(sums, "sum")                       # per-GPU {sum z, sum z^2} added over NVLink (NCCL all-reduce)
+            ops.unary("sqrt", t_sumsq, t_sumsq)              # norm2 in place, one small launch of the library
 
     def barrier():
         if world > 1:
@@ -635,6 +642,8 @@ def run_ours(args):
         stop.record()
         final_dev = sums.clone()                              # {sum, norm2} of the last timed step
         barrier()
+        if peer is not None:
+            peer.check()                                      # no exchange gave up waiting for a peer
         # keep the GPU under the same load until a few more samples exist.  The loop is bounded by the clock, so its
         # trip count differs between ranks: it must not contain a collective (the kernel alone is the load).
         t_end = time.time() + 0.6
@@ -739,7 +748,10 @@ def run_ours(args):
             "dtype": "f32", "data": "synthetic",
             "config": {"workload": WORKLOAD,
                        "elements": n_total, "elements_per_gpu": per, "l2": "inputs (%.1f GiB per GPU) far larger than the 126 MB L2" % (8 * per / 2 ** 30),
-                       "hash_seed": [1, 2]},
+                       "hash_seed": [1, 2],
+                       "exchange": ("none (one GPU)" if world == 1 else
+                                    "one kernel over peer memory: pairs stored into every peer's buffer, added in rank order, square root"
+                                    if peer is not None else "NCCL all-reduce of the pair, then the square root")},
             "frac_of_8tbs_per_gpu": value / (world * NOMINAL_HBM_GBS),
             "frac_of_measured_copy_per_gpu": value / (world * peak),
             "elements_per_s": n_total / (ms_step * 1e-3),
@@ -761,7 +773,8 @@ def run_ours(args):
                             "scalars are read back and compared with a float64 evaluation of what was streamed "
                             "(`checked`).  h2d_gbs_per_rank_bare is the same two buffers copied with nothing else "
                             "running on the rank, all ranks at once: the ceiling this number can reach."},
-            # per step: the streaming kernel, the fold of its partial sums, the square root
+            # per step: the streaming kernel, the fold of its partial sums, and the exchange kernel (sum over the GPUs
+            # and square root) or, with one GPU or on the NCCL route, the square root kernel
             "gpu_launches": 3 * args.steps * world,
             "clocks": cl,
         }

@@ -431,6 +431,29 @@ SOLID_API int solid_gpu_reduce_all_device(const char *op, int dtype, SOLID_GPU_A
                                           void *result, void *buffer, cudaStream_t stream);
 
 /* ------------------------------------------------------------------------ */
+/* Sum of a pair of per-GPU partial results over the GPUs of one node through  */
+/* peer memory: the exchange at the end of a sharded reduction (sum, norm2) as  */
+/* ONE small kernel instead of a library all-reduce.  No counterpart in the     */
+/* reference, which has no collectives (its only cross-device traffic is         */
+/* cudaMemcpyPeerAsync, src/core/gpu/storage_gpu.c:140-143).                     */
+/*   - every GPU provides a zero-initialised exchange buffer of                  */
+/*     solid_gpu_peer_sum_buffer_size(world) bytes that all the others can      */
+/*     address (peer access, CUDA IPC or symmetric memory); buffers[r] is GPU   */
+/*     r's buffer as mapped in the calling process, buffers[rank] its own;      */
+/*   - sequence is 1, 2, 3, ... and the same on every GPU for the same exchange;*/
+/*   - local holds count (1 or 2) floats on this GPU; result receives the sums  */
+/*     over all GPUs, added in rank order (the same bits everywhere), with the  */
+/*     square root taken of value i when bit i of sqrt_mask is set;             */
+/*   - the wait for the peers is bounded: after limit_us microseconds (0: two   */
+/*     seconds) the kernel sets *status (device int, may be NULL) to 1 and      */
+/*     returns; result is then meaningless and the buffers must be zeroed and   */
+/*     the sequence restarted before the next use.                              */
+SOLID_API size_t solid_gpu_peer_sum_buffer_size(int world);
+SOLID_API int solid_gpu_peer_sum_float(int world, int rank, void *const *buffers, unsigned int sequence, int count,
+                                       const float *local, float *result, int sqrt_mask, unsigned int limit_us,
+                                       int *status, cudaStream_t stream);
+
+/* ------------------------------------------------------------------------ */
 /* Axis sum of float tensors for callers that may not allocate.  It has no    */
 /* counterpart in the reference.  Some callers cannot obtain device memory at  */
 /* the point where they reduce: a callback or destructor that runs while an    */

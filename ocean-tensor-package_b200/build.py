@@ -32,7 +32,7 @@ TYPES = {"bool": 0, "uint8": 1, "uint16": 1, "uint32": 1, "uint64": 1,
          "int8": 2, "int16": 2, "int32": 2, "int64": 2,
          "half": 3, "float": 3, "double": 3, "chalf": 4, "cfloat": 4, "cdouble": 4}
 PER_TYPE_UNITS = ["reduce", "copy", "unary", "binary", "fill", "steps"]     # slowest first
-SINGLE_UNITS = ["base", "luts", "reduce_plan", "fused", "noalloc", "index", "gemm"]
+SINGLE_UNITS = ["base", "luts", "reduce_plan", "fused", "noalloc", "index", "gemm", "peer"]
 
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-std=c++17", "-O3", "-lineinfo",
               "--fmad=false",            # one rounding per operation, as the CPU oracle computes

@@ -25,16 +25,17 @@ namespace sd {
 // axpy + sums
 // ===========================================================================
 #ifndef AX_THREADS_N
-#define AX_THREADS_N 512
+#define AX_THREADS_N 256
 #endif
 #ifndef AX_VECTORS
-#define AX_VECTORS 2
+#define AX_VECTORS 4
 #endif
-// 512 threads x 2 vectors per operand: the same 16 KB of x per block as 256 x 4, measured 1 % faster on 2^30 floats
-// (7159 against 7091 GB/s; 256 x 2: 7061, 256 x 8: 7076, 128 x 4: 7039, 512 x 4: 7109, 1024 x 2: 5849).
+// 256 threads x 4 vectors per operand (16 KB of x per block).  Other shapes on 2^30 floats, stand-alone: 256 x 2 7061,
+// 256 x 8 7076, 128 x 4 7039, 512 x 4 7109, 512 x 2 7159, 1024 x 2 5849 against 7091 GB/s; 512 x 2 was then tried in
+// the bench and was 0.2-0.4 % SLOWER there (7.269 against 7.258 ms on 2^32 elements), so the shape stayed.
 constexpr int AX_THREADS = AX_THREADS_N;
 constexpr int AX_U = AX_VECTORS;             // 16-byte vectors per thread and operand
-constexpr int AX_FOLD = 4096;                // per-block pairs folded into one second-level pair
+constexpr int AX_FOLD = 1024;                // per-block pairs folded into one second-level pair
 
 template <class T> struct Sums { T s, s2; };
 
@@ -43,10 +44,19 @@ template <class T> struct Sums { T s, s2; };
 template <class T>
 SD_D Sums<T> axpy_fold(const Sums<T> *part, uint64_t count, Sums<T> *smem)
 {
+   // Four pairs per thread are fetched before any is added (one load per pair): the fold is a chain of memory
+   // latencies, not of bandwidth.  The order of the additions is fixed by the indices alone.
+   using Pair = typename chunk_of<sizeof(Sums<T>) >= 16 ? 16 : 8>::type;
+   static_assert(sizeof(Sums<T>) == sizeof(Pair), "a pair is one 8- or 16-byte access");
    T s = 0, s2 = 0;
-   for (uint64_t i = threadIdx.x; i < count; i += AX_THREADS) {
-      const T ps = __ldcg(&part[i].s), ps2 = __ldcg(&part[i].s2);      // possibly written by other blocks: past the L1 cache
-      s += ps; s2 += ps2;
+   for (uint64_t i = threadIdx.x; i < count; i += 4 * AX_THREADS) {
+      Pair raw[4];
+#pragma unroll
+      for (int k = 0; k < 4; k++)                                        // possibly written by other blocks: past the L1 cache
+         if (i + (uint64_t)k * AX_THREADS < count) raw[k] = __ldcg(reinterpret_cast<const Pair *>(part + i + (uint64_t)k * AX_THREADS));
+#pragma unroll
+      for (int k = 0; k < 4; k++)
+         if (i + (uint64_t)k * AX_THREADS < count) { Sums<T> v; memcpy(&v, &raw[k], sizeof(v)); s += v.s; s2 += v.s2; }
    }
 #pragma unroll
    for (int d = 16; d >= 1; d >>= 1) {

@@ -282,6 +282,20 @@ class SolidGPU:
         self._check(f(C.c_size_t(n), scalar_from_bytes(a), C.c_void_p(x), C.c_void_p(y), C.c_void_p(z),
                       C.c_void_p(sums), C.c_void_p(partials), C.c_void_p(stream)), "axpy_sums_%s" % dtype)
 
+    def peer_sum_buffer_size(self, world: int) -> int:
+        f = self.fn("solid_gpu_peer_sum_buffer_size")
+        f.restype = C.c_size_t
+        return int(f(C.c_int(world)))
+
+    def peer_sum_float(self, world, rank, buffers, sequence, count, local, result, sqrt_mask=0, limit_us=0,
+                       status=0, stream=0):
+        """buffers: device addresses of every rank's exchange buffer as mapped in this process."""
+        arr = (C.c_void_p * world)(*[C.c_void_p(int(b)) for b in buffers])
+        self._check(self.fn("solid_gpu_peer_sum_float")(C.c_int(world), C.c_int(rank), arr, C.c_uint(sequence), C.c_int(count),
+                                                        C.c_void_p(local), C.c_void_p(result), C.c_int(sqrt_mask),
+                                                        C.c_uint(limit_us), C.c_void_p(status), C.c_void_p(stream)),
+                    "peer_sum_float")
+
     def mixed_multiply_add(self, size, operands, ctype, stream=0):
         """operands: four tuples (ptr, strides, dtype name, byteswapped) for a, b, c, dst."""
         ops, keep = [], []
