@@ -230,9 +230,11 @@ __global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedPa
       const uint64_t rows = udiv64(p.relem, rowlen);
       const uint64_t total = rows * nslot;
       constexpr int U = sizeof(T) >= 4 ? 8 : 4;         // vectors in flight per thread (measured: 8 is slower for 1-byte types)
-      // slots per split, rounded up to whole iterations of the dense loop (trailing splits may be empty)
+      // slots per split, rounded up to whole passes of the group (trailing splits may be empty).  Rounding to whole
+      // iterations of the unrolled loop instead left 80 of 592 blocks without work on 2^24 floats (2048 iterations of
+      // 32 KB over 592 blocks: four each for 512 of them), 17.6 us where an even split takes 15.
       uint64_t chunk = udiv64(total + p.split - 1, p.split);
-      chunk = udiv64(chunk + (uint64_t)group * U - 1, (uint64_t)group * U) * ((uint64_t)group * U);
+      chunk = udiv64(chunk + (uint64_t)group - 1, (uint64_t)group) * (uint64_t)group;
       const uint64_t begin = (uint64_t)s * chunk < total ? (uint64_t)s * chunk : total;
       const uint64_t end = begin + chunk < total ? begin + chunk : total;
       uint64_t slot0 = begin + lane;
@@ -248,6 +250,22 @@ __global__ void __launch_bounds__(RED_THREADS, 4) red_row(const R r, const RedPa
             for (int u = 0; u < U; u++) v[u] = ld_vec<T, VEC>(q + u * gstep);
 #pragma unroll
             for (int u = 0; u < U; u++) accum_vec<R, T, VEC>(r, acc, v[u]);
+         }
+         if (U >= 8 && slot0 + (uint64_t)3 * group < fend) {        // the remainder in halves of the unroll factor
+            Vec<T, VEC> v[4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) v[u] = ld_vec<T, VEC>(q + u * gstep);
+#pragma unroll
+            for (int u = 0; u < 4; u++) accum_vec<R, T, VEC>(r, acc, v[u]);
+            slot0 += (uint64_t)group * 4; q += gstep * 4;
+         }
+         if (slot0 + (uint64_t)group < fend) {
+            Vec<T, VEC> v[2];
+#pragma unroll
+            for (int u = 0; u < 2; u++) v[u] = ld_vec<T, VEC>(q + u * gstep);
+#pragma unroll
+            for (int u = 0; u < 2; u++) accum_vec<R, T, VEC>(r, acc, v[u]);
+            slot0 += (uint64_t)group * 2; q += gstep * 2;
          }
          for (; slot0 < fend; slot0 += group, q += gstep) accum_vec<R, T, VEC>(r, acc, ld_vec<T, VEC>(q));
          // the ragged last slot (fewer than VEC elements) is left to the general loop below
