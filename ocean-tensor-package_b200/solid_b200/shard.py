@@ -109,10 +109,14 @@ def finish_norm2(sumsq):
     return math.sqrt(float(sumsq))
 
 
-def sharded_axpy_sums(a, x, y, z=None, sums=None, group=None):
+def sharded_axpy_sums(a, x, y, z=None, sums=None, group=None, peer=None):
     """z = a*x + y on this rank's shard with sum(z) and sum(z*z) combined over all ranks.
-    Returns (z, sums) with sums = {sum(z), sum(z*z)} of the WHOLE tensor on every rank (device)."""
+    Returns (z, sums) with sums = {sum(z), sum(z*z)} of the WHOLE tensor on every rank (device); with a PeerSum
+    the pairs are exchanged through peer memory, else by the collective."""
     from . import ops
     z, sums = ops.axpy_sums(a, x, y, z, sums)
-    combine(sums, "sum", group)
+    if peer is not None:
+        peer.sum_pair(sums)
+    else:
+        combine(sums, "sum", group)
     return z, sums
