@@ -119,6 +119,70 @@ __global__ void __launch_bounds__(IX_THREADS) index_kernel(const IndexParams p, 
    }
 }
 
+// Whole runs along dimension 0 (A[:, perm], A[:, :, idx], ...): dimension 0 carries no table and both tensors are
+// contiguous along it, so each position of the other dimensions is a run of size[0] elements that is copied as
+// bytes.  A block owns one piece of one run: the run's two offsets (table look-ups included) are computed once per
+// block instead of once per group of four elements, and the piece moves as 16-byte accesses when both of its ends are
+// 16-byte aligned (a property of table entries, so it is tested on the device, uniformly for the block), else element
+// by element.  The element-wise kernel above spends some fifty instructions per element on such selections (a
+// gather of 32 KB runs ran at 3.5 TB/s).
+constexpr int IXR_U = 4;                                       // 16-byte pieces per thread
+template <int CS, int NC, int MODE>
+__global__ void __launch_bounds__(IX_THREADS) index_runs_kernel(const IndexParams p, const uint4 value16, const uint32_t pieces)
+{
+   constexpr int ES = CS * NC;
+   // block -> (run, piece)
+   const uint32_t run = blockIdx.x / pieces, piece = blockIdx.x - run * pieces;
+   int64_t o1 = 0, o2 = 0;
+   {  uint64_t r = run;
+      for (int d = 1; d < p.ndims; d++) {
+         const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
+         const int64_t *tab = p.offsets[d];
+         o1 += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
+         if (MODE != IX_FILL) o2 += (int64_t)c * p.stride2[d];
+      }
+   }
+   const uint64_t bytes = (uint64_t)p.size[0] * ES;
+   const uint64_t span = (uint64_t)IX_THREADS * IXR_U * 16;    // bytes per piece
+   const uint64_t first = (uint64_t)piece * span;
+   const uint64_t len = bytes - first < span ? bytes - first : span;
+   char *q1 = p.ptr1 + o1 + first;
+   char *q2 = (MODE != IX_FILL) ? p.ptr2 + o2 + first : nullptr;
+   const bool wide = ((reinterpret_cast<uintptr_t>(q1) | (MODE != IX_FILL ? reinterpret_cast<uintptr_t>(q2) : 0)) & 15u) == 0;
+   if (wide) {
+      const uint64_t nvec = len / 16;
+      uint4 v[IXR_U];
+#pragma unroll
+      for (int u = 0; u < IXR_U; u++) {
+         const uint64_t i = (uint64_t)u * IX_THREADS + threadIdx.x;
+         if (MODE == IX_FILL) v[u] = value16;
+         else if (i < nvec) v[u] = __ldcs(reinterpret_cast<const uint4 *>(MODE == IX_GET ? q1 : q2) + i);
+      }
+#pragma unroll
+      for (int u = 0; u < IXR_U; u++) {
+         const uint64_t i = (uint64_t)u * IX_THREADS + threadIdx.x;
+         if (i < nvec) __stcs(reinterpret_cast<uint4 *>(MODE == IX_GET ? q2 : q1) + i, v[u]);
+      }
+      // the last bytes of the run (fewer than 16), byte by byte
+      const uint64_t done = nvec * 16;
+      if (done + threadIdx.x < len) {
+         const uint64_t i = done + threadIdx.x;
+         if (MODE == IX_FILL) q1[i] = reinterpret_cast<const char *>(&value16)[i % ES];
+         else if (MODE == IX_GET) q2[i] = q1[i];
+         else q1[i] = q2[i];
+      }
+   } else {
+      // component by component (the tensors and the table entries are aligned to the components)
+      using C = typename raw_comp<CS>::type;
+      const uint64_t n = len / CS;
+      for (uint64_t i = threadIdx.x; i < n; i += IX_THREADS) {
+         if (MODE == IX_FILL) reinterpret_cast<C *>(q1)[i] = reinterpret_cast<const C *>(&value16)[i % (16 / CS)];
+         else if (MODE == IX_GET) reinterpret_cast<C *>(q2)[i] = reinterpret_cast<const C *>(q1)[i];
+         else reinterpret_cast<C *>(q1)[i] = reinterpret_cast<const C *>(q2)[i];
+      }
+   }
+}
+
 template <int CS, int NC, int MODE>
 int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptrdiff_t *strides1, void *ptr1,
                  const ptrdiff_t *strides2, void *ptr2, const solid_scalar *value, cudaStream_t stream)
@@ -138,6 +202,20 @@ int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptr
    if (!aligned_to(ptr1, CS) || (MODE != IX_FILL && !aligned_to(ptr2, CS))) SD_ERROR("Tensor data must be aligned to the element size");
    RawElem<CS, NC> v; memset(&v, 0, sizeof(v));
    if (value) memcpy(&v, value, sizeof(v));
+   // whole runs along dimension 0 (no table there, both sides contiguous, at least 1 KB long): copied as bytes
+   if (ndims > 0 && (offsets == nullptr || offsets[0] == nullptr) && p.stride1[0] == ES &&
+       (MODE == IX_FILL || p.stride2[0] == ES) && (uint64_t)size[0] * ES >= 1024) {
+      const uint64_t span = (uint64_t)IX_THREADS * IXR_U * 16;
+      const uint64_t pieces = ((uint64_t)size[0] * ES + span - 1) / span;
+      const uint64_t runs = p.nelem / (uint64_t)size[0];
+      if (pieces <= 0xFFFFFFFFull && runs * pieces <= 0x7FFFFFFFull) {
+         uint4 value16;
+         for (int i = 0; i < 16 / ES; i++) memcpy(reinterpret_cast<char *>(&value16) + i * ES, &v, ES);
+         index_runs_kernel<CS, NC, MODE><<<(unsigned)(runs * pieces), IX_THREADS, 0, stream>>>(p, value16, (uint32_t)pieces);
+         SD_LAUNCH_CHECK();
+         return 0;
+      }
+   }
    // groups of V along dimension 0: the dense-strided side must be contiguous there and 16-byte aligned everywhere
    bool vec = V > 1 && ndims > 0 && size[0] % V == 0;
    if (vec && MODE != IX_FILL) {

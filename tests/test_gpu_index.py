@@ -35,6 +35,15 @@ def index_cases(dtype, rng):
     cases.append(("strided", [8, 7], [None, None], [es, 40 * es], [40, 30]))
     cases.append(("empty", [0, 30], [np.zeros(0, dtype=np.int64), None], [0, 40 * es], [40, 30]))
     cases.append(("scalar", [], [], [], [3]))
+    # whole runs along dimension 0 (no table there, at least 1 KB long): columns picked by a table; the second case
+    # has runs of more than one 16 KB piece for the wider types and starts that are not 16-byte aligned
+    src = [1100, 20]
+    cases.append(("runs", [1100, 13], [None, rng.permutation(20)[:13].astype(np.int64) * 1100 * es], [es, 0], src))
+    src = [5003, 9]
+    cases.append(("long_runs", [5003, 5], [None, rng.permutation(9)[:5].astype(np.int64) * 5003 * es], [es, 0], src))
+    src = [1030, 3, 6]
+    cases.append(("runs_3d", [1030, 3, 4], [None, None, rng.permutation(6)[:4].astype(np.int64) * 3090 * es],
+                  [es, 1030 * es, 0], src))
     return cases
 
 
