@@ -44,6 +44,14 @@ def index_cases(dtype, rng):
     src = [1030, 3, 6]
     cases.append(("runs_3d", [1030, 3, 4], [None, None, rng.permutation(6)[:4].astype(np.int64) * 3090 * es],
                   [es, 1030 * es, 0], src))
+    # gathers along dimension 0 into a destination that is contiguous there: a span that fits the shared-memory
+    # window (any alignment of its first byte), one that does not (for elements of 2 bytes and more), and a long 1-d one
+    src = [400, 7]
+    cases.append(("gather0", [300, 7], [rng.permutation(400)[:300].astype(np.int64) * es, None], [0, 400 * es], src))
+    src = [40000, 3]
+    cases.append(("gather0_wide", [300, 3], [np.sort(rng.permutation(40000)[:300]).astype(np.int64) * es, None], [0, 40000 * es], src))
+    src = [9000]
+    cases.append(("gather0_1d", [8500], [(rng.permutation(9000)[:8500].astype(np.int64)) * es], [0], src))
     return cases
 
 
