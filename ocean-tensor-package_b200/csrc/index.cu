@@ -185,45 +185,50 @@ __global__ void __launch_bounds__(IX_THREADS) index_runs_kernel(const IndexParam
 
 // Gather ALONG dimension 0 (A[perm, :]: a table on dimension 0, the destination contiguous there).  Element
 // gathers from global memory are bound by the load unit (up to 32 sectors per warp instruction: the general kernel
-// ran 4-byte gathers at 2.9 TB/s).  Here a block owns up to IXG_ROWS positions of one run of the destination.  It
-// reads its slice of the table once to find the span of source bytes the slice addresses; when that span fits the
-// shared-memory window (a permutation of a column, a sort, a shuffle within a block of rows) it is fetched with
-// coalesced 16-byte loads and the gather runs on shared memory; otherwise the block gathers from global memory
-// directly.  Either way the table is read with coalesced 8-byte loads and the destination written with coalesced
-// stores, and the offsets of the other dimensions are computed once per block.
+// ran 4-byte gathers at 2.9 TB/s).  Here a block owns up to IXG_ROWS positions of dimension 0 for IXG_RUNS
+// consecutive runs of the destination.  It reads its slice of the table to find the span of source bytes the slice
+// addresses; when that span fits the shared-memory window (a permutation of a column, a sort, a shuffle within a
+// block of rows) the slice is kept in registers as 32-bit offsets from its lowest entry and, run by run, the span
+// is fetched with coalesced 16-byte loads and the gather runs on shared memory; otherwise the block gathers from
+// global memory directly.  The table (8 bytes per 4-byte element of ONE run) is so read twice per IXG_RUNS runs
+// instead of twice per run, which was what bounded the one-run form (80 us on 4-byte gathers within 32 KB columns).
+// Measured on that case (8192 x 4096 floats): 256 threads with 4 / 8 / 16 runs per block 69.8 / 68.3 / 65.9 us (16 runs
+// leave fewer blocks than the GPU holds), 512 threads 80-83 us, 1024 threads 101-106 us, three resident blocks by a
+// register cap (80 registers, spills) 78-82 us.
+#ifndef IXG_THREADS_N
+#define IXG_THREADS_N 256
+#endif
+#ifndef IXG_RUNS_N
+#define IXG_RUNS_N 8
+#endif
+constexpr int IXG_T = IXG_THREADS_N;                           // threads of a block
 constexpr int IXG_ROWS = 8192;                                 // positions of dimension 0 per block
-constexpr int IXG_WINDOW = 64 * 1024;                          // bytes of the source a block may stage
+constexpr int IXG_PER = IXG_ROWS / IXG_T;                      // ... per thread: their table entries stay in registers
+constexpr int IXG_RUNS = IXG_RUNS_N;                           // runs (positions of the other dimensions) a block serves with them
+constexpr int IXG_WINDOW = 64 * 1024;                          // bytes of the source a block may stage per run
+#ifndef IXG_MINB
+#define IXG_MINB 2             // two resident blocks (128 registers): without the request the compiler takes more and one block fits
+#endif
 template <int CS, int NC>
-__global__ void __launch_bounds__(IX_THREADS) index_gather0_kernel(const IndexParams p, const uint32_t chunks)
+__global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const IndexParams p, const uint32_t chunks, const uint64_t runs)
 {
    constexpr int ES = CS * NC;
+   constexpr int GU = IXG_PER < 8 ? IXG_PER : 8;                                      // loads a thread has in flight
    using C = typename raw_comp<CS>::type;
    extern __shared__ __align__(16) unsigned char ixg_smem[];
-   __shared__ long long red_lo[IX_THREADS / 32], red_hi[IX_THREADS / 32];
-   const uint32_t run = blockIdx.x / chunks, chunk = blockIdx.x - run * chunks;
-   int64_t o1 = 0, o2 = 0;
-   {  uint64_t r = run;
-      for (int d = 1; d < p.ndims; d++) {
-         const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
-         const int64_t *tab = p.offsets[d];
-         o1 += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
-         o2 += (int64_t)c * p.stride2[d];
-      }
-   }
+   __shared__ long long red_lo[IXG_T / 32], red_hi[IXG_T / 32];
+   const uint32_t rgroup = blockIdx.x / chunks, chunk = blockIdx.x - rgroup * chunks;
    const uint64_t r0 = (uint64_t)chunk * IXG_ROWS;
    const uint32_t n = (uint64_t)p.size[0] - r0 < (uint64_t)IXG_ROWS ? (uint32_t)((uint64_t)p.size[0] - r0) : (uint32_t)IXG_ROWS;
    const int64_t *tab0 = p.offsets[0] + r0;
-   const char *src = p.ptr1 + o1;
-   char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
-   // span of the slice
+   // span of the slice of the table
    long long lo = 0x7FFFFFFFFFFFFFFFll, hi = -0x7FFFFFFFFFFFFFFFll - 1;
-   constexpr int GU = 8;                                       // table entries (and gathers) a thread has in flight
-   for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IX_THREADS * GU) {
+   for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IXG_T * GU) {
       long long t[GU];
 #pragma unroll
-      for (int u = 0; u < GU; u++) { const uint32_t i = i0 + u * IX_THREADS; t[u] = i < n ? __ldg(tab0 + i) : lo; }
+      for (int u = 0; u < GU; u++) { const uint32_t i = i0 + u * IXG_T; t[u] = i < n ? __ldg(tab0 + i) : lo; }
 #pragma unroll
-      for (int u = 0; u < GU; u++) { lo = t[u] < lo ? t[u] : lo; hi = (i0 + u * IX_THREADS < n && t[u] > hi) ? t[u] : hi; }
+      for (int u = 0; u < GU; u++) { lo = t[u] < lo ? t[u] : lo; hi = (i0 + u * IXG_T < n && t[u] > hi) ? t[u] : hi; }
    }
 #pragma unroll
    for (int d = 16; d >= 1; d >>= 1) {
@@ -233,64 +238,86 @@ __global__ void __launch_bounds__(IX_THREADS) index_gather0_kernel(const IndexPa
    if ((threadIdx.x & 31) == 0) { red_lo[threadIdx.x >> 5] = lo; red_hi[threadIdx.x >> 5] = hi; }
    __syncthreads();
 #pragma unroll
-   for (int w = 0; w < IX_THREADS / 32; w++) { lo = red_lo[w] < lo ? red_lo[w] : lo; hi = red_hi[w] > hi ? red_hi[w] : hi; }
+   for (int w = 0; w < IXG_T / 32; w++) { lo = red_lo[w] < lo ? red_lo[w] : lo; hi = red_hi[w] > hi ? red_hi[w] : hi; }
    const unsigned long long span = (unsigned long long)(hi - lo) + ES;
-   if (span <= (unsigned long long)IXG_WINDOW) {
-      // stage [lo, hi + ES): shared-memory byte `pad + k` mirrors source byte `lo + k`, so that 16-byte chunks line up
-      const char *first = src + lo;
-      const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(first) & 15u);
-      const uint32_t total = pad + (uint32_t)span;                               // end of the mirrored bytes
-      const uint32_t head_end = pad == 0 ? 0u : (16u < total ? 16u : total);     // bytes [pad, head_end): before the first whole chunk
-      const uint32_t body_end = total & ~15u;                                    // whole chunks end here
-      const char *abase = first - pad;                                           // 16-byte aligned
-      for (uint32_t k0 = (pad == 0 ? 0u : 16u) + threadIdx.x * 16u; k0 + 16u <= body_end; k0 += IX_THREADS * 16u * 4u) {
-         uint4 w[4];
+   const bool staged = span <= (unsigned long long)IXG_WINDOW;
+   // the slice as 32-bit offsets from its lowest entry, in registers for all the runs of this block
+   uint32_t rel[IXG_PER];
+   if (staged) {
 #pragma unroll
-         for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IX_THREADS * 16u; if (k + 16u <= body_end) w[u] = __ldg(reinterpret_cast<const uint4 *>(abase + k)); }
-#pragma unroll
-         for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IX_THREADS * 16u; if (k + 16u <= body_end) *reinterpret_cast<uint4 *>(ixg_smem + k) = w[u]; }
-      }
-      for (uint32_t k = pad + threadIdx.x * CS; k < head_end; k += IX_THREADS * CS)
-         *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
-      const uint32_t tail_from = body_end > head_end ? body_end : head_end;
-      for (uint32_t k = tail_from + threadIdx.x * CS; k < total; k += IX_THREADS * CS)
-         *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
-      __syncthreads();
-      for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IX_THREADS * GU) {
-         long long t[GU]; RawElem<CS, NC> e[GU];
-#pragma unroll
-         for (int u = 0; u < GU; u++) { const uint32_t i = i0 + u * IX_THREADS; t[u] = i < n ? __ldg(tab0 + i) : lo; }
-#pragma unroll
-         for (int u = 0; u < GU; u++) {
-            const C *q = reinterpret_cast<const C *>(ixg_smem + pad + (uint32_t)(t[u] - lo));
-#pragma unroll
-            for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
-         }
-#pragma unroll
-         for (int u = 0; u < GU; u++) {
-            const uint32_t i = i0 + u * IX_THREADS;
-            if (i < n) { C *o = reinterpret_cast<C *>(dst + (uint64_t)i * ES);
-#pragma unroll
-               for (int k = 0; k < NC; k++) o[k] = e[u].c[k]; }
+      for (int j = 0; j < IXG_PER; j++) { const uint32_t i = threadIdx.x + j * IXG_T; rel[j] = i < n ? (uint32_t)(__ldg(tab0 + i) - lo) : 0u; }
+   }
+   for (int g = 0; g < IXG_RUNS; g++) {
+      const uint64_t run = (uint64_t)rgroup * IXG_RUNS + g;
+      if (run >= runs) break;
+      int64_t o1 = 0, o2 = 0;
+      {  uint64_t r = run;
+         for (int d = 1; d < p.ndims; d++) {
+            const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
+            const int64_t *tab = p.offsets[d];
+            o1 += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
+            o2 += (int64_t)c * p.stride2[d];
          }
       }
-   } else {
-      for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IX_THREADS * GU) {
-         long long t[GU]; RawElem<CS, NC> e[GU];
+      const char *src = p.ptr1 + o1;
+      char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
+      if (staged) {
+         // stage [lo, hi + ES): shared-memory byte `pad + k` mirrors source byte `lo + k`, so that 16-byte chunks line up
+         const char *first = src + lo;
+         const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(first) & 15u);
+         const uint32_t total = pad + (uint32_t)span;                               // end of the mirrored bytes
+         const uint32_t head_end = pad == 0 ? 0u : (16u < total ? 16u : total);     // bytes [pad, head_end): before the first whole chunk
+         const uint32_t body_end = total & ~15u;                                    // whole chunks end here
+         const char *abase = first - pad;                                           // 16-byte aligned
+         if (g > 0) __syncthreads();                                                // the previous run's gathers are done
+         for (uint32_t k0 = (pad == 0 ? 0u : 16u) + threadIdx.x * 16u; k0 + 16u <= body_end; k0 += IXG_T * 16u * 4u) {
+            uint4 w[4];
 #pragma unroll
-         for (int u = 0; u < GU; u++) { const uint32_t i = i0 + u * IX_THREADS; t[u] = i < n ? __ldg(tab0 + i) : lo; }
+            for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IXG_T * 16u; if (k + 16u <= body_end) w[u] = __ldg(reinterpret_cast<const uint4 *>(abase + k)); }
 #pragma unroll
-         for (int u = 0; u < GU; u++) {
-            const C *q = reinterpret_cast<const C *>(src + t[u]);
-#pragma unroll
-            for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
+            for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IXG_T * 16u; if (k + 16u <= body_end) *reinterpret_cast<uint4 *>(ixg_smem + k) = w[u]; }
          }
+         for (uint32_t k = pad + threadIdx.x * CS; k < head_end; k += IXG_T * CS)
+            *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
+         const uint32_t tail_from = body_end > head_end ? body_end : head_end;
+         for (uint32_t k = tail_from + threadIdx.x * CS; k < total; k += IXG_T * CS)
+            *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
+         __syncthreads();
 #pragma unroll
-         for (int u = 0; u < GU; u++) {
-            const uint32_t i = i0 + u * IX_THREADS;
-            if (i < n) { C *o = reinterpret_cast<C *>(dst + (uint64_t)i * ES);
+         for (int j0 = 0; j0 < IXG_PER; j0 += GU) {
+            RawElem<CS, NC> e[GU];
 #pragma unroll
-               for (int k = 0; k < NC; k++) o[k] = e[u].c[k]; }
+            for (int u = 0; u < GU; u++) {
+               const C *q = reinterpret_cast<const C *>(ixg_smem + pad + rel[j0 + u]);
+#pragma unroll
+               for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
+            }
+#pragma unroll
+            for (int u = 0; u < GU; u++) {
+               const uint32_t i = threadIdx.x + (j0 + u) * IXG_T;
+               if (i < n) { C *o = reinterpret_cast<C *>(dst + (uint64_t)i * ES);
+#pragma unroll
+                  for (int k = 0; k < NC; k++) o[k] = e[u].c[k]; }
+            }
+         }
+      } else {
+         for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IXG_T * GU) {
+            long long t[GU]; RawElem<CS, NC> e[GU];
+#pragma unroll
+            for (int u = 0; u < GU; u++) { const uint32_t i = i0 + u * IXG_T; t[u] = i < n ? __ldg(tab0 + i) : lo; }
+#pragma unroll
+            for (int u = 0; u < GU; u++) {
+               const C *q = reinterpret_cast<const C *>(src + t[u]);
+#pragma unroll
+               for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
+            }
+#pragma unroll
+            for (int u = 0; u < GU; u++) {
+               const uint32_t i = i0 + u * IXG_T;
+               if (i < n) { C *o = reinterpret_cast<C *>(dst + (uint64_t)i * ES);
+#pragma unroll
+                  for (int k = 0; k < NC; k++) o[k] = e[u].c[k]; }
+            }
          }
       }
    }
@@ -333,14 +360,15 @@ int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptr
    if (MODE == IX_GET && ndims > 0 && offsets != nullptr && offsets[0] != nullptr && p.stride2[0] == ES && size[0] >= 256) {
       const uint64_t chunks = ((uint64_t)size[0] + IXG_ROWS - 1) / IXG_ROWS;
       const uint64_t runs = p.nelem / (uint64_t)size[0];
-      if (chunks <= 0xFFFFFFFFull && runs * chunks <= 0x7FFFFFFFull) {
+      const uint64_t rgroups = (runs + IXG_RUNS - 1) / IXG_RUNS;
+      if (chunks <= 0xFFFFFFFFull && rgroups * chunks <= 0x7FFFFFFFull) {
          static bool attr_set = false;
          const size_t smem = IXG_WINDOW + 16;
          if (!attr_set) {
             SD_CUDA_CHECK(cudaFuncSetAttribute(index_gather0_kernel<CS, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set = true;
          }
-         index_gather0_kernel<CS, NC><<<(unsigned)(runs * chunks), IX_THREADS, smem, stream>>>(p, (uint32_t)chunks);
+         index_gather0_kernel<CS, NC><<<(unsigned)(rgroups * chunks), IXG_T, smem, stream>>>(p, (uint32_t)chunks, runs);
          SD_LAUNCH_CHECK();
          return 0;
       }
