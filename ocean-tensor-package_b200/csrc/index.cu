@@ -194,7 +194,8 @@ __global__ void __launch_bounds__(IX_THREADS) index_runs_kernel(const IndexParam
 // instead of twice per run, which was what bounded the one-run form (80 us on 4-byte gathers within 32 KB columns).
 // Measured on that case (8192 x 4096 floats): 256 threads with 4 / 8 / 16 runs per block 69.8 / 68.3 / 65.9 us (16 runs
 // leave fewer blocks than the GPU holds), 512 threads 80-83 us, 1024 threads 101-106 us, three resident blocks by a
-// register cap (80 registers, spills) 78-82 us.
+// register cap (80 registers, spills; also with the offsets packed two per register) 78-82 us; the copy of the next
+// run's span overlapping the gather of this one (two buffers of 32 KB) 72 -> 70 us.
 #ifndef IXG_THREADS_N
 #define IXG_THREADS_N 256
 #endif
@@ -247,48 +248,61 @@ __global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const In
 #pragma unroll
       for (int j = 0; j < IXG_PER; j++) { const uint32_t i = threadIdx.x + j * IXG_T; rel[j] = i < n ? (uint32_t)(__ldg(tab0 + i) - lo) : 0u; }
    }
-   for (int g = 0; g < IXG_RUNS; g++) {
-      const uint64_t run = (uint64_t)rgroup * IXG_RUNS + g;
-      if (run >= runs) break;
-      int64_t o1 = 0, o2 = 0;
-      {  uint64_t r = run;
-         for (int d = 1; d < p.ndims; d++) {
-            const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
-            const int64_t *tab = p.offsets[d];
-            o1 += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
-            o2 += (int64_t)c * p.stride2[d];
-         }
+   // offsets of run g of this block in the indexed tensor and in the destination
+   auto run_offsets = [&](int g, int64_t &o1, int64_t &o2) -> bool {
+      uint64_t r = (uint64_t)rgroup * IXG_RUNS + g;
+      if (g >= IXG_RUNS || r >= runs) return false;
+      o1 = 0; o2 = 0;
+      for (int d = 1; d < p.ndims; d++) {
+         const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
+         const int64_t *tab = p.offsets[d];
+         o1 += tab ? __ldg(tab + c) : (int64_t)c * p.stride1[d];
+         o2 += (int64_t)c * p.stride2[d];
       }
-      const char *src = p.ptr1 + o1;
-      char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
-      if (staged) {
-         // stage [lo, hi + ES): shared-memory byte `pad + k` mirrors source byte `lo + k`, so that 16-byte chunks line up
-         const char *first = src + lo;
+      return true;
+   };
+   if (staged) {
+      // Shared-memory byte `pad + k` of a buffer mirrors source byte `lo + k` of the run, so that 16-byte chunks line
+      // up.  Whole chunks travel with cp.async (no registers, the copy of the NEXT run's span overlaps the gather of
+      // this one when two spans fit the window), the ragged head and tail with ordinary accesses.
+      const bool two = span <= (unsigned long long)(IXG_WINDOW / 2);        // each half is IXG_WINDOW / 2 + 16 bytes, pad < 16
+      auto stage = [&](int64_t o1, unsigned char *buf) -> uint32_t {
+         const char *first = p.ptr1 + o1 + lo;
          const uint32_t pad = (uint32_t)(reinterpret_cast<uintptr_t>(first) & 15u);
          const uint32_t total = pad + (uint32_t)span;                               // end of the mirrored bytes
          const uint32_t head_end = pad == 0 ? 0u : (16u < total ? 16u : total);     // bytes [pad, head_end): before the first whole chunk
          const uint32_t body_end = total & ~15u;                                    // whole chunks end here
          const char *abase = first - pad;                                           // 16-byte aligned
-         if (g > 0) __syncthreads();                                                // the previous run's gathers are done
-         for (uint32_t k0 = (pad == 0 ? 0u : 16u) + threadIdx.x * 16u; k0 + 16u <= body_end; k0 += IXG_T * 16u * 4u) {
-            uint4 w[4];
-#pragma unroll
-            for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IXG_T * 16u; if (k + 16u <= body_end) w[u] = __ldg(reinterpret_cast<const uint4 *>(abase + k)); }
-#pragma unroll
-            for (int u = 0; u < 4; u++) { const uint32_t k = k0 + u * IXG_T * 16u; if (k + 16u <= body_end) *reinterpret_cast<uint4 *>(ixg_smem + k) = w[u]; }
-         }
+         const uint32_t sbase = (uint32_t)__cvta_generic_to_shared(buf);
+         for (uint32_t k = (pad == 0 ? 0u : 16u) + threadIdx.x * 16u; k + 16u <= body_end; k += IXG_T * 16u)
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" :: "r"(sbase + k), "l"(abase + k) : "memory");
+         asm volatile("cp.async.commit_group;" ::: "memory");
          for (uint32_t k = pad + threadIdx.x * CS; k < head_end; k += IXG_T * CS)
-            *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
+            *reinterpret_cast<C *>(buf + k) = *reinterpret_cast<const C *>(abase + k);
          const uint32_t tail_from = body_end > head_end ? body_end : head_end;
          for (uint32_t k = tail_from + threadIdx.x * CS; k < total; k += IXG_T * CS)
-            *reinterpret_cast<C *>(ixg_smem + k) = *reinterpret_cast<const C *>(abase + k);
+            *reinterpret_cast<C *>(buf + k) = *reinterpret_cast<const C *>(abase + k);
+         return pad;
+      };
+      unsigned char *bufs[2] = { ixg_smem, two ? ixg_smem + IXG_WINDOW / 2 + 16 : ixg_smem };
+      int64_t o1 = 0, o2 = 0, n1 = 0, n2 = 0;
+      bool have = run_offsets(0, o1, o2);
+      uint32_t pad = have ? stage(o1, bufs[0]) : 0u;
+      for (int g = 0; have; g++) {
+         // with two buffers the next run's span is requested before this one is consumed
+         bool next = run_offsets(g + 1, n1, n2);
+         uint32_t npad = 0;
+         if (next && two) { npad = stage(n1, bufs[(g + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+         else asm volatile("cp.async.wait_group 0;" ::: "memory");
          __syncthreads();
+         const unsigned char *buf = bufs[g & 1];
+         char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
 #pragma unroll
          for (int j0 = 0; j0 < IXG_PER; j0 += GU) {
             RawElem<CS, NC> e[GU];
 #pragma unroll
             for (int u = 0; u < GU; u++) {
-               const C *q = reinterpret_cast<const C *>(ixg_smem + pad + rel[j0 + u]);
+               const C *q = reinterpret_cast<const C *>(buf + pad + rel[j0 + u]);
 #pragma unroll
                for (int k = 0; k < NC; k++) e[u].c[k] = q[k];
             }
@@ -300,7 +314,16 @@ __global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const In
                   for (int k = 0; k < NC; k++) o[k] = e[u].c[k]; }
             }
          }
-      } else {
+         __syncthreads();                                      // this buffer may be overwritten from now on
+         if (next && !two) npad = stage(n1, bufs[0]);
+         have = next; o1 = n1; o2 = n2; pad = npad;
+      }
+   } else {
+      for (int g = 0; g < IXG_RUNS; g++) {
+         int64_t o1, o2;
+         if (!run_offsets(g, o1, o2)) break;
+         const char *src = p.ptr1 + o1;
+         char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
          for (uint32_t i0 = threadIdx.x; i0 < n; i0 += IXG_T * GU) {
             long long t[GU]; RawElem<CS, NC> e[GU];
 #pragma unroll
@@ -363,7 +386,7 @@ int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptr
       const uint64_t rgroups = (runs + IXG_RUNS - 1) / IXG_RUNS;
       if (chunks <= 0xFFFFFFFFull && rgroups * chunks <= 0x7FFFFFFFull) {
          static bool attr_set = false;
-         const size_t smem = IXG_WINDOW + 16;
+         const size_t smem = IXG_WINDOW + 32;                   // one span of up to 64 KB, or two of up to 32 KB, each with its alignment pad
          if (!attr_set) {
             SD_CUDA_CHECK(cudaFuncSetAttribute(index_gather0_kernel<CS, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set = true;
