@@ -185,12 +185,12 @@ __global__ void __launch_bounds__(IX_THREADS) index_runs_kernel(const IndexParam
 
 // Gather ALONG dimension 0 (A[perm, :]: a table on dimension 0, the destination contiguous there).  Element
 // gathers from global memory are bound by the load unit (up to 32 sectors per warp instruction: the general kernel
-// ran 4-byte gathers at 2.9 TB/s).  Here a block owns up to IXG_ROWS positions of dimension 0 for IXG_RUNS
-// consecutive runs of the destination.  It reads its slice of the table to find the span of source bytes the slice
+// ran 4-byte gathers at 2.9 TB/s).  Here a block owns up to IXG_ROWS positions of dimension 0 for an even share of
+// the runs of the destination (the grid is one resident wave, or fewer blocks with at least IXG_RUNS runs each).  It reads its slice of the table to find the span of source bytes the slice
 // addresses; when that span fits the shared-memory window (a permutation of a column, a sort, a shuffle within a
 // block of rows) the slice is kept in registers as 32-bit offsets from its lowest entry and, run by run, the span
 // is fetched with coalesced 16-byte loads and the gather runs on shared memory; otherwise the block gathers from
-// global memory directly.  The table (8 bytes per 4-byte element of ONE run) is so read twice per IXG_RUNS runs
+// global memory directly.  The table (8 bytes per 4-byte element of ONE run) is so read twice per block
 // instead of twice per run, which was what bounded the one-run form (80 us on 4-byte gathers within 32 KB columns).
 // Measured on that case (8192 x 4096 floats): 256 threads with 4 / 8 / 16 runs per block 69.8 / 68.3 / 65.9 us (16 runs
 // leave fewer blocks than the GPU holds), 512 threads 80-83 us, 1024 threads 101-106 us, three resident blocks by a
@@ -205,20 +205,23 @@ __global__ void __launch_bounds__(IX_THREADS) index_runs_kernel(const IndexParam
 constexpr int IXG_T = IXG_THREADS_N;                           // threads of a block
 constexpr int IXG_ROWS = 8192;                                 // positions of dimension 0 per block
 constexpr int IXG_PER = IXG_ROWS / IXG_T;                      // ... per thread: their table entries stay in registers
-constexpr int IXG_RUNS = IXG_RUNS_N;                           // runs (positions of the other dimensions) a block serves with them
+constexpr int IXG_RUNS = IXG_RUNS_N;                           // fewest runs (positions of the other dimensions) a block serves with them
 constexpr int IXG_WINDOW = 64 * 1024;                          // bytes of the source a block may stage per run
 #ifndef IXG_MINB
 #define IXG_MINB 2             // two resident blocks (128 registers): without the request the compiler takes more and one block fits
 #endif
 template <int CS, int NC>
-__global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const IndexParams p, const uint32_t chunks, const uint64_t runs)
+__global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const IndexParams p, const uint32_t chunks, const uint64_t runs,
+                                                                        const uint32_t shares)
 {
    constexpr int ES = CS * NC;
    constexpr int GU = IXG_PER < 8 ? IXG_PER : 8;                                      // loads a thread has in flight
    using C = typename raw_comp<CS>::type;
    extern __shared__ __align__(16) unsigned char ixg_smem[];
    __shared__ long long red_lo[IXG_T / 32], red_hi[IXG_T / 32];
-   const uint32_t rgroup = blockIdx.x / chunks, chunk = blockIdx.x - rgroup * chunks;
+   // block -> (share of the runs, chunk of dimension 0); share k of `shares` covers runs [k * runs / shares, (k + 1) * runs / shares)
+   const uint32_t share = blockIdx.x / chunks, chunk = blockIdx.x - share * chunks;
+   const uint64_t run_begin = (uint64_t)share * runs / shares, run_end = (uint64_t)(share + 1) * runs / shares;
    const uint64_t r0 = (uint64_t)chunk * IXG_ROWS;
    const uint32_t n = (uint64_t)p.size[0] - r0 < (uint64_t)IXG_ROWS ? (uint32_t)((uint64_t)p.size[0] - r0) : (uint32_t)IXG_ROWS;
    const int64_t *tab0 = p.offsets[0] + r0;
@@ -250,8 +253,8 @@ __global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const In
    }
    // offsets of run g of this block in the indexed tensor and in the destination
    auto run_offsets = [&](int g, int64_t &o1, int64_t &o2) -> bool {
-      uint64_t r = (uint64_t)rgroup * IXG_RUNS + g;
-      if (g >= IXG_RUNS || r >= runs) return false;
+      uint64_t r = run_begin + (uint64_t)g;
+      if (r >= run_end) return false;
       o1 = 0; o2 = 0;
       for (int d = 1; d < p.ndims; d++) {
          const uint64_t q = udiv64(r, (uint64_t)p.size[d]), c = r - q * (uint64_t)p.size[d]; r = q;
@@ -284,18 +287,19 @@ __global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const In
             *reinterpret_cast<C *>(buf + k) = *reinterpret_cast<const C *>(abase + k);
          return pad;
       };
-      unsigned char *bufs[2] = { ixg_smem, two ? ixg_smem + IXG_WINDOW / 2 + 16 : ixg_smem };
+      const uint32_t second = two ? (uint32_t)(IXG_WINDOW / 2 + 16) : 0u;        // offset of the second buffer (none: the same)
+      auto buffer = [&](int g) -> unsigned char * { return ixg_smem + ((g & 1) ? second : 0u); };
       int64_t o1 = 0, o2 = 0, n1 = 0, n2 = 0;
       bool have = run_offsets(0, o1, o2);
-      uint32_t pad = have ? stage(o1, bufs[0]) : 0u;
+      uint32_t pad = have ? stage(o1, buffer(0)) : 0u;
       for (int g = 0; have; g++) {
          // with two buffers the next run's span is requested before this one is consumed
          bool next = run_offsets(g + 1, n1, n2);
          uint32_t npad = 0;
-         if (next && two) { npad = stage(n1, bufs[(g + 1) & 1]); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
+         if (next && two) { npad = stage(n1, buffer(g + 1)); asm volatile("cp.async.wait_group 1;" ::: "memory"); }
          else asm volatile("cp.async.wait_group 0;" ::: "memory");
          __syncthreads();
-         const unsigned char *buf = bufs[g & 1];
+         const unsigned char *buf = buffer(g);
          char *dst = p.ptr2 + o2 + (int64_t)r0 * ES;
 #pragma unroll
          for (int j0 = 0; j0 < IXG_PER; j0 += GU) {
@@ -315,11 +319,11 @@ __global__ void __launch_bounds__(IXG_T, IXG_MINB) index_gather0_kernel(const In
             }
          }
          __syncthreads();                                      // this buffer may be overwritten from now on
-         if (next && !two) npad = stage(n1, bufs[0]);
+         if (next && !two) npad = stage(n1, buffer(0));
          have = next; o1 = n1; o2 = n2; pad = npad;
       }
    } else {
-      for (int g = 0; g < IXG_RUNS; g++) {
+      for (int g = 0; ; g++) {
          int64_t o1, o2;
          if (!run_offsets(g, o1, o2)) break;
          const char *src = p.ptr1 + o1;
@@ -383,15 +387,21 @@ int index_launch(int ndims, const size_t *size, solid_int64 **offsets, const ptr
    if (MODE == IX_GET && ndims > 0 && offsets != nullptr && offsets[0] != nullptr && p.stride2[0] == ES && size[0] >= 256) {
       const uint64_t chunks = ((uint64_t)size[0] + IXG_ROWS - 1) / IXG_ROWS;
       const uint64_t runs = p.nelem / (uint64_t)size[0];
-      const uint64_t rgroups = (runs + IXG_RUNS - 1) / IXG_RUNS;
-      if (chunks <= 0xFFFFFFFFull && rgroups * chunks <= 0x7FFFFFFFull) {
+      // one resident wave of blocks: each keeps its slice of the table for an even share of the runs (at least
+      // IXG_RUNS of them, so that the two passes over the slice are spread over several runs)
+      DeviceInfo dev;
+      if (current_device_info(&dev) != 0) return -1;
+      uint64_t shares = (uint64_t)dev.sms * IXG_MINB / chunks;
+      if (shares > (runs + IXG_RUNS - 1) / IXG_RUNS) shares = (runs + IXG_RUNS - 1) / IXG_RUNS;
+      if (shares < 1) shares = 1;
+      if (chunks <= 0xFFFFFFFFull && shares * chunks <= 0x7FFFFFFFull) {
          static bool attr_set = false;
          const size_t smem = IXG_WINDOW + 32;                   // one span of up to 64 KB, or two of up to 32 KB, each with its alignment pad
          if (!attr_set) {
             SD_CUDA_CHECK(cudaFuncSetAttribute(index_gather0_kernel<CS, NC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
             attr_set = true;
          }
-         index_gather0_kernel<CS, NC><<<(unsigned)(rgroups * chunks), IXG_T, smem, stream>>>(p, (uint32_t)chunks, runs);
+         index_gather0_kernel<CS, NC><<<(unsigned)(shares * chunks), IXG_T, smem, stream>>>(p, (uint32_t)chunks, runs, (uint32_t)shares);
          SD_LAUNCH_CHECK();
          return 0;
       }
