@@ -30,6 +30,11 @@ def test_shard_ranges_tile_the_axis():
         shard.combine(None, "median")
 
 
+def test_peer_exchange_is_not_offered_without_a_process_group():
+    # the peer-memory exchange needs an initialised NCCL group of at least two ranks; otherwise callers use combine()
+    assert shard.PeerSum.create("cpu") is None
+
+
 def _worker(rank, world, port, n, q):
     sys.path[:0] = [str(ROOT), str(ROOT / "ocean-tensor-package_b200")]
     import torch
