@@ -70,6 +70,8 @@ class PeerSum:
         lib = _lib.get()
         world, rank = dist.get_world_size(group), dist.get_rank(group)
         ok, made = 1, None
+        # the exchange uses plain peer stores only: keep the buffers off NVLink multicast objects
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
         try:
             import torch.distributed._symmetric_memory as symm_mem
             nbytes = lib.peer_sum_buffer_size(world)
