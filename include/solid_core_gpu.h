@@ -437,7 +437,7 @@ SOLID_API int solid_gpu_reduce_all_device(const char *op, int dtype, SOLID_GPU_A
 /* reference, which has no collectives (its only cross-device traffic is         */
 /* cudaMemcpyPeerAsync, src/core/gpu/storage_gpu.c:140-143).                     */
 /*   - every GPU provides a zero-initialised exchange buffer of                  */
-/*     solid_gpu_peer_sum_buffer_size(world) bytes that all the others can      */
+/*     solid_gpu_peer_sum_buffer_size(world, &bytes) bytes that the others can  */
 /*     address (peer access, CUDA IPC or symmetric memory); buffers[r] is GPU   */
 /*     r's buffer as mapped in the calling process, buffers[rank] its own;      */
 /*   - sequence is 1, 2, 3, ... and the same on every GPU for the same exchange;*/
@@ -448,7 +448,7 @@ SOLID_API int solid_gpu_reduce_all_device(const char *op, int dtype, SOLID_GPU_A
 /*     seconds) the kernel sets *status (device int, may be NULL) to 1 and      */
 /*     returns; result is then meaningless and the buffers must be zeroed and   */
 /*     the sequence restarted before the next use.                              */
-SOLID_API size_t solid_gpu_peer_sum_buffer_size(int world);
+SOLID_API int solid_gpu_peer_sum_buffer_size(int world, size_t *size);
 SOLID_API int solid_gpu_peer_sum_float(int world, int rank, void *const *buffers, unsigned int sequence, int count,
                                        const float *local, float *result, int sqrt_mask, unsigned int limit_us,
                                        int *status, cudaStream_t stream);

@@ -71,8 +71,13 @@ __global__ void __launch_bounds__(32) peer_sum_kernel(const PeerSumParams p)
 }
 } // namespace sd
 
-extern "C" size_t solid_gpu_peer_sum_buffer_size(int world)
-{  return world > 0 ? (size_t)2 * (size_t)world * 16 : 0; }
+extern "C" int solid_gpu_peer_sum_buffer_size(int world, size_t *size)
+{
+   if (size == nullptr) SD_ERROR("peer_sum_buffer_size needs a result pointer");
+   if (world < 1 || world > sd::PEER_MAX) SD_ERROR("peer_sum: between 1 and %d GPUs (got %d)", sd::PEER_MAX, world);
+   *size = (size_t)2 * (size_t)world * 16;                      // two sets of one 16-byte slot per GPU
+   return 0;
+}
 
 extern "C" int solid_gpu_peer_sum_float(int world, int rank, void *const *buffers, unsigned int sequence, int count,
                                         const float *local, float *result, int sqrt_mask, unsigned int limit_us,

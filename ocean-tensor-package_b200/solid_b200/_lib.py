@@ -283,9 +283,9 @@ class SolidGPU:
                       C.c_void_p(sums), C.c_void_p(partials), C.c_void_p(stream)), "axpy_sums_%s" % dtype)
 
     def peer_sum_buffer_size(self, world: int) -> int:
-        f = self.fn("solid_gpu_peer_sum_buffer_size")
-        f.restype = C.c_size_t
-        return int(f(C.c_int(world)))
+        out = C.c_size_t(0)
+        self._check(self.fn("solid_gpu_peer_sum_buffer_size")(C.c_int(world), C.byref(out)), "peer_sum_buffer_size")
+        return out.value
 
     def peer_sum_float(self, world, rank, buffers, sequence, count, local, result, sqrt_mask=0, limit_us=0,
                        status=0, stream=0):
